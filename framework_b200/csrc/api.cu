@@ -1,0 +1,642 @@
+// C ABI of libmni_b200.so: argument checking, view classification, path selection and
+// scratch management.  All arithmetic happens in the kernels of gemm_tcgen05.cu,
+// skinny.cu and pointwise.cu; there is no host or library (cuBLAS) fallback.
+#include "internal.h"
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <mutex>
+#include <vector>
+
+namespace mni {
+
+std::atomic<uint64_t> g_launches{0};
+
+namespace {
+
+thread_local char t_error[512] = "";
+
+__device__ unsigned int g_err_word;   // first timeout code recorded by any kernel of the library
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+    std::mutex mu;
+    bool init = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    uint8_t *ws = nullptr;        // library-owned scratch
+    size_t ws_bytes = 0;
+    uint8_t *user_ws = nullptr;   // caller-provided scratch (takes precedence)
+    size_t user_bytes = 0;
+    unsigned int *err_word = nullptr;
+};
+DeviceState g_dev[kMaxDevices];
+
+int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+// Bump allocator over the device's scratch.  In dry mode nothing is touched: the
+// same host logic runs and only the byte count is produced (workspace_query).
+struct Arena {
+    DeviceState *st = nullptr;
+    bool dry = false;
+    size_t used = 0;
+    std::vector<std::pair<size_t, size_t>> blocks;   // (offset, bytes) in request order
+    size_t reserve(size_t bytes) {
+        const size_t off = used;
+        used += (bytes + 255) & ~static_cast<size_t>(255);
+        return off;
+    }
+};
+
+int device_state(DeviceState **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(MNI_B200_ERR_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(MNI_B200_ERR_DEVICE, "device ordinal %d out of range", dev);
+    DeviceState &st = g_dev[dev];
+    if (!st.init) {
+        cudaDeviceProp prop;
+        e = cudaGetDeviceProperties(&prop, dev);
+        if (e != cudaSuccess) return fail(MNI_B200_ERR_DEVICE, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+        if (prop.major != 10)
+            return fail(MNI_B200_ERR_DEVICE,
+                        "device %d is compute capability %d.%d; this library only carries sm_100a code", dev,
+                        prop.major, prop.minor);
+        st.sm_count = prop.multiProcessorCount;
+        st.cc_major = prop.major;
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_err_word);
+        if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        st.err_word = static_cast<unsigned int *>(p);
+        e = cudaMemset(st.err_word, 0, sizeof(unsigned int));
+        if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "cudaMemset: %s", cudaGetErrorString(e));
+        st.init = true;
+    }
+    *out = &st;
+    return MNI_B200_OK;
+}
+
+// Makes `bytes` of scratch available and returns its base.
+int scratch_base(DeviceState &st, size_t bytes, uint8_t **base) {
+    if (st.user_ws) {
+        if (bytes > st.user_bytes)
+            return fail(MNI_B200_ERR_WORKSPACE, "caller-provided scratch holds %zu bytes, %zu needed", st.user_bytes,
+                        bytes);
+        *base = st.user_ws;
+        return MNI_B200_OK;
+    }
+    if (bytes > st.ws_bytes) {
+        const size_t want = bytes + bytes / 4 + (1u << 20);
+        if (st.ws) {
+            // cudaFree waits for work that may still read the old buffer.
+            cudaError_t e = cudaFree(st.ws);
+            st.ws = nullptr;
+            st.ws_bytes = 0;
+            if (e != cudaSuccess) return fail(MNI_B200_ERR_WORKSPACE, "cudaFree(scratch): %s", cudaGetErrorString(e));
+        }
+        void *p = nullptr;
+        cudaError_t e = cudaMalloc(&p, want);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(MNI_B200_ERR_WORKSPACE, "cudaMalloc(%zu) for scratch failed: %s", want, cudaGetErrorString(e));
+        }
+        st.ws = static_cast<uint8_t *>(p);
+        st.ws_bytes = want;
+    }
+    *base = st.ws;
+    return MNI_B200_OK;
+}
+
+// ------------------------------------------------------------------ shapes
+int64_t prod(const int64_t *s, int n) {
+    int64_t p = 1;
+    for (int i = 0; i < n; ++i) p *= s[i];
+    return p;
+}
+
+// utils.rs:3-20
+int broadcast_shape(const int64_t *a, int an, const int64_t *b, int bn, int64_t *out) {
+    const int nd = std::max(an, bn);
+    for (int i = 0; i < nd; ++i) {
+        const int64_t da = i < nd - an ? 1 : a[i - (nd - an)];
+        const int64_t db = i < nd - bn ? 1 : b[i - (nd - bn)];
+        if (da == db) out[i] = da;
+        else if (da == 1) out[i] = db;
+        else if (db == 1) out[i] = da;
+        else return -1;
+    }
+    return nd;
+}
+
+int check_view(const mni_b200_view *v, const char *name, int min_nd) {
+    if (!v) return fail(MNI_B200_ERR_ARG, "%s is null", name);
+    if (v->ndim < min_nd) return fail(MNI_B200_ERR_NDIM, "matmul requires at least 2D tensors (%s has %d)", name, v->ndim);
+    if (v->ndim > MNI_B200_MAX_DIMS) return fail(MNI_B200_ERR_ARG, "%s has %d dims (max %d)", name, v->ndim, MNI_B200_MAX_DIMS);
+    for (int d = 0; d < v->ndim; ++d) {
+        if (v->shape[d] < 0 || v->stride[d] < 0) return fail(MNI_B200_ERR_ARG, "%s has a negative extent or stride", name);
+        if (v->shape[d] > 0x7fffffffLL) return fail(MNI_B200_ERR_TOO_LARGE, "%s dim %d = %lld exceeds 2^31-1", name, d, (long long)v->shape[d]);
+    }
+    if (!v->ptr && prod(v->shape, v->ndim) > 0) return fail(MNI_B200_ERR_ARG, "%s has a null data pointer", name);
+    return MNI_B200_OK;
+}
+
+// A matrix operand read through a TMA descriptor.  `transposed` selects which of the
+// view's last two dims is the contraction dim: false -> [.., rows, k], true -> [.., k, rows].
+// Returns false if the view cannot be described (then the caller packs it first).
+bool view_to_operand(const mni_b200_view &v, bool transposed, Operand &op) {
+    const int nd = v.ndim;
+    const int64_t s_r = transposed ? v.stride[nd - 1] : v.stride[nd - 2];
+    const int64_t s_k = transposed ? v.stride[nd - 2] : v.stride[nd - 1];
+    op.ptr = v.ptr;
+    op.rows = transposed ? v.shape[nd - 1] : v.shape[nd - 2];
+    op.kdim = transposed ? v.shape[nd - 2] : v.shape[nd - 1];
+    if ((reinterpret_cast<uintptr_t>(v.ptr) & 15) != 0) return false;
+    const bool k_ok = (s_k == 1 || op.kdim == 1) && (op.rows == 1 || (s_r > 0 && s_r % 4 == 0));
+    const bool mn_ok = (s_r == 1 || op.rows == 1) && (op.kdim == 1 || (s_k > 0 && s_k % 4 == 0));
+    if (k_ok) {
+        op.k_major = true;
+        op.ld = s_r;
+    } else if (mn_ok) {
+        op.k_major = false;
+        op.ld = s_k;
+    } else {
+        return false;
+    }
+    // Batch dims: drop extent-1 dims, merge dims that are contiguous with each other.
+    int64_t bs[MNI_B200_MAX_DIMS], bt[MNI_B200_MAX_DIMS];
+    int nb = 0;
+    op.batch = 1;
+    for (int d = 0; d < nd - 2; ++d) {
+        op.batch *= v.shape[d];
+        if (v.shape[d] == 1) continue;
+        if (nb > 0 && bt[nb - 1] == v.stride[d] * v.shape[d]) {
+            bs[nb - 1] *= v.shape[d];
+            bt[nb - 1] = v.stride[d];
+        } else {
+            bs[nb] = v.shape[d];
+            bt[nb] = v.stride[d];
+            ++nb;
+        }
+    }
+    if (nb > 3) return false;
+    for (int i = 0; i < 3; ++i) { op.bshape[i] = 1; op.bstride[i] = 0; }
+    for (int i = 0; i < nb; ++i) {
+        if (bt[i] <= 0 || bt[i] % 4 != 0) return false;
+        if (bs[i] > 0x7fffffffLL) return false;
+        op.bshape[3 - nb + i] = bs[i];
+        op.bstride[3 - nb + i] = bt[i];
+    }
+    return true;
+}
+
+struct Call {
+    DeviceState *st;
+    Arena arena;
+    cudaStream_t stream;
+    uint32_t flags;
+    uint8_t *base = nullptr;   // resolved scratch base (real mode, second pass)
+    bool dry() const { return arena.dry; }
+    float *at(size_t off) const { return reinterpret_cast<float *>(base + off); }
+};
+
+// Gathers a view into scratch as [batch_flat, R, C] with the last dim padded to a multiple of 4.
+int pack_view(Call &c, const mni_b200_view &v, mni_b200_view *packed, size_t *offset) {
+    const int nd = v.ndim;
+    const int64_t cols = v.shape[nd - 1], rows = v.shape[nd - 2];
+    const int64_t ld = std::max<int64_t>(4, round_up(cols, 4));
+    const int64_t batch = prod(v.shape, nd - 2);
+    const size_t bytes = static_cast<size_t>(batch * rows * ld) * sizeof(float);
+    const size_t off = c.arena.reserve(bytes);
+    *offset = off;
+    packed->ndim = 3;
+    packed->shape[0] = batch; packed->shape[1] = rows; packed->shape[2] = cols;
+    packed->stride[0] = rows * ld; packed->stride[1] = ld; packed->stride[2] = 1;
+    packed->ptr = c.dry() ? reinterpret_cast<const float *>(static_cast<uintptr_t>(256)) : c.at(off);
+    if (c.dry()) return MNI_B200_OK;
+    return launch_pack(v, c.at(off), ld, c.stream);
+}
+
+// Operand from a view, packing it into scratch when TMA cannot describe it.
+int make_operand(Call &c, const mni_b200_view &v, bool transposed, Operand &op) {
+    const bool force_pack = (c.flags & MNI_B200_FORCE_PACK) != 0;
+    if (!force_pack && view_to_operand(v, transposed, op)) return MNI_B200_OK;
+    mni_b200_view packed;
+    size_t off;
+    int rc = pack_view(c, v, &packed, &off);
+    if (rc) return rc;
+    if (!view_to_operand(packed, transposed, op)) return fail(MNI_B200_ERR_ARG, "packed operand is not describable");
+    // The packed copy is flat in the batch: keep the original flat batch count.
+    return MNI_B200_OK;
+}
+
+int run_gemm(Call &c, GemmProblem &p) {
+    p.fast_tf32 = (c.flags & MNI_B200_PRECISION_TF32) != 0;
+    p.force_splits = static_cast<int>((c.flags >> 16) & 0xffu);
+    if (p.M > 0x7fffffffLL || p.N > 0x7fffffffLL || p.K > 0x7fffffffLL || p.batch * p.fold > 0x7fffffffLL ||
+        p.batch * ((p.M + 127) / 128) * ((p.N + 63) / 64) > 0x3fffffffLL)
+        return fail(MNI_B200_ERR_TOO_LARGE, "GEMM %lld x %lld x %lld (batch %lld) exceeds the kernels' int32 indexing",
+                    (long long)p.M, (long long)p.N, (long long)p.K, (long long)p.batch);
+    const size_t pbytes = gemm_tc_partial_bytes(p, c.st->sm_count);
+    size_t poff = 0;
+    if (pbytes) poff = c.arena.reserve(pbytes);
+    if (c.dry()) return MNI_B200_OK;
+    return launch_gemm_tc(p, pbytes ? c.at(poff) : nullptr, c.st->err_word, c.st->sm_count, c.stream);
+}
+
+int zero_or_bias_fill(Call &c, float *out, int64_t rows, int64_t n, const float *bias, bool accumulate) {
+    if (c.dry() || rows * n == 0) return MNI_B200_OK;
+    if (!accumulate) MNI_CUDA(cudaMemsetAsync(out, 0, static_cast<size_t>(rows * n) * sizeof(float), c.stream));
+    if (bias) return launch_add_bias(out, bias, out, rows, n, c.stream);
+    return MNI_B200_OK;
+}
+
+struct Shapes {
+    int64_t M, K, N;
+    int64_t out_batch[MNI_B200_MAX_DIMS];
+    int out_nb;
+    int64_t batch, a_batch, b_batch;
+};
+
+int analyse(const mni_b200_view *a, const mni_b200_view *b, Shapes &s) {
+    int rc = check_view(a, "a", 2);
+    if (rc) return rc;
+    rc = check_view(b, "b", 2);
+    if (rc) return rc;
+    s.M = a->shape[a->ndim - 2];
+    s.K = a->shape[a->ndim - 1];
+    s.N = b->shape[b->ndim - 1];
+    if (b->shape[b->ndim - 2] != s.K)
+        return fail(MNI_B200_ERR_INNER_DIM, "matmul inner dimensions must match: %lld vs %lld", (long long)s.K,
+                    (long long)b->shape[b->ndim - 2]);
+    s.out_nb = broadcast_shape(a->shape, a->ndim - 2, b->shape, b->ndim - 2, s.out_batch);
+    if (s.out_nb < 0) return fail(MNI_B200_ERR_BROADCAST, "batch shapes are not broadcastable");
+    s.batch = prod(s.out_batch, s.out_nb);
+    s.a_batch = prod(a->shape, a->ndim - 2);
+    s.b_batch = prod(b->shape, b->ndim - 2);
+    return MNI_B200_OK;
+}
+
+// ------------------------------------------------------------------ forward
+int fwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, float *out, const float *bias) {
+    Shapes s;
+    int rc = analyse(a, b, s);
+    if (rc) return rc;
+    if (!out && s.batch * s.M * s.N > 0) return fail(MNI_B200_ERR_ARG, "c is null");
+    const bool accumulate = (c.flags & MNI_B200_ACCUMULATE_C) != 0;
+    if (s.batch * s.M * s.N == 0) return MNI_B200_OK;
+    if (s.K == 0) return zero_or_bias_fill(c, out, s.batch * s.M, s.N, bias, accumulate);
+
+    const bool want_skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
+                             ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 16);
+    if (want_skinny && s.batch == 1 && skinny_fwd_supported(s.M, s.N, s.K)) {
+        const int an = a->ndim, bn = b->ndim;
+        const bool a_ok = a->stride[an - 1] == 1 || s.K == 1;
+        const bool b_ok = (b->stride[bn - 1] == 1 || s.N == 1) && (b->stride[bn - 2] % 4 == 0 || s.K == 1) &&
+                          (reinterpret_cast<uintptr_t>(b->ptr) & 15) == 0;
+        if (a_ok && b_ok) {
+            const size_t pbytes = skinny_fwd_partial_bytes(s.M, s.N, s.K, c.st->sm_count);
+            const size_t poff = c.arena.reserve(pbytes);
+            if (c.dry()) return MNI_B200_OK;
+            const int64_t ldw = s.K == 1 ? round_up(s.N, 4) : b->stride[bn - 2];
+            return launch_skinny_fwd(a->ptr, a->stride[an - 2], b->ptr, ldw, out, s.N, bias, accumulate, s.M, s.N,
+                                     s.K, c.at(poff), c.st->sm_count, c.stream);
+        }
+    }
+
+    GemmProblem p;
+    rc = make_operand(c, *a, false, p.A);
+    if (rc) return rc;
+    rc = make_operand(c, *b, true, p.B);
+    if (rc) return rc;
+    p.A.batch = s.a_batch;
+    p.B.batch = s.b_batch;
+    p.M = s.M; p.N = s.N; p.K = s.K;
+    p.batch = s.batch;
+    p.fold = 1;
+    p.C = out;
+    p.ldc = s.N;
+    p.c_bstride = s.M * s.N;
+    p.bias = bias;
+    p.accumulate = accumulate;
+    return run_gemm(c, p);
+}
+
+// ------------------------------------------------------------------ backward
+// One gradient: G[ob.., R, Cn] = X . Y (a GEMM over `kdim`) reduced to `target`'s shape.
+//   X supplies the rows, Y the columns; both already as Operands with flat batch counts.
+int grad_gemm(Call &c, Operand X, Operand Y, int64_t R, int64_t Cn, int64_t kdim, const int64_t *ob, int onb,
+              const mni_b200_view &target, float *out, bool accumulate) {
+    const int64_t obatch = prod(ob, onb);
+    const int tnb = target.ndim - 2;
+    const int64_t tbatch = prod(target.shape, tnb);
+    bool same = true;
+    {   // target batch dims, right-aligned against ob, all equal?
+        if (tnb > onb) same = false;
+        for (int i = 0; same && i < onb; ++i) {
+            const int64_t td = i < onb - tnb ? 1 : target.shape[i - (onb - tnb)];
+            if (td != ob[i]) same = false;
+        }
+    }
+    GemmProblem p;
+    p.A = X; p.B = Y;
+    p.M = R; p.N = Cn; p.K = kdim;
+    p.bias = nullptr;
+    if (same || obatch == 1) {
+        p.batch = obatch; p.fold = 1;
+        p.C = out; p.ldc = Cn; p.c_bstride = R * Cn; p.accumulate = accumulate;
+        return run_gemm(c, p);
+    }
+    if (tbatch == 1) {
+        // The operand was broadcast over every batch: sum the batches inside the contraction.
+        p.batch = 1; p.fold = obatch;
+        p.C = out; p.ldc = Cn; p.c_bstride = R * Cn; p.accumulate = accumulate;
+        return run_gemm(c, p);
+    }
+    // Partial broadcast: full batched product into scratch, then the device-side unbroadcast.
+    const size_t bytes = static_cast<size_t>(obatch * R * Cn) * sizeof(float);
+    const size_t off = c.arena.reserve(bytes);
+    p.batch = obatch; p.fold = 1;
+    p.C = c.dry() ? nullptr : c.at(off);
+    p.ldc = Cn; p.c_bstride = R * Cn; p.accumulate = false;
+    int rc = run_gemm(c, p);
+    if (rc || c.dry()) return rc;
+    int64_t gshape[MNI_B200_MAX_DIMS + 2];
+    for (int i = 0; i < onb; ++i) gshape[i] = ob[i];
+    gshape[onb] = R; gshape[onb + 1] = Cn;
+    return launch_unbroadcast(c.at(off), gshape, onb + 2, target.shape, target.ndim, out, accumulate, c.stream);
+}
+
+int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_b200_view *dc, float *da,
+             float *db, float *dbias) {
+    Shapes s;
+    int rc = analyse(a, b, s);
+    if (rc) return rc;
+    rc = check_view(dc, "dc", 2);
+    if (rc) return rc;
+    const int gn = dc->ndim;
+    if (dc->shape[gn - 2] != s.M || dc->shape[gn - 1] != s.N)
+        return fail(MNI_B200_ERR_ARG, "dc is [.., %lld, %lld] but the forward output is [.., %lld, %lld]",
+                    (long long)dc->shape[gn - 2], (long long)dc->shape[gn - 1], (long long)s.M, (long long)s.N);
+    const int64_t g_batch = prod(dc->shape, gn - 2);
+    const bool acc_da = (c.flags & MNI_B200_ACCUMULATE_DA) != 0;
+    const bool acc_db = (c.flags & MNI_B200_ACCUMULATE_DB) != 0;
+    const bool acc_dbias = (c.flags & MNI_B200_ACCUMULATE_DBIAS) != 0;
+    const int64_t a_elems = s.a_batch * s.M * s.K, b_elems = s.b_batch * s.K * s.N;
+
+    if (dbias) {
+        // Column sums over every row of dc (ops/elementwise.rs:224-229 via utils::unbroadcast).
+        const int64_t rows = g_batch * s.M;
+        if (rows == 0 || s.N == 0) {
+            rc = zero_or_bias_fill(c, dbias, 1, s.N, nullptr, acc_dbias);
+            if (rc) return rc;
+        } else {
+            mni_b200_view flat = *dc;
+            const float *src = dc->ptr;
+            int64_t ld = s.N;
+            bool contiguous = true;
+            {
+                int64_t expect = 1;
+                for (int d = gn - 1; d >= 0; --d) {
+                    if (dc->shape[d] != 1 && dc->stride[d] != expect) contiguous = false;
+                    expect *= dc->shape[d];
+                }
+            }
+            if (!contiguous) {
+                size_t off;
+                rc = pack_view(c, *dc, &flat, &off);
+                if (rc) return rc;
+                src = flat.ptr;
+                ld = flat.stride[1];
+            }
+            const size_t pbytes = colsum_partial_bytes(rows, s.N, c.st->sm_count);
+            const size_t poff = c.arena.reserve(pbytes);
+            if (!c.dry()) {
+                rc = launch_colsum(src, ld, dbias, rows, s.N, acc_dbias, c.at(poff), c.st->sm_count, c.stream);
+                if (rc) return rc;
+            }
+        }
+    }
+
+    // grad_a = unbroadcast(dc . b^T, a.shape)   (ops/matmul.rs:231-240)
+    if (da && a_elems > 0) {
+        if (s.N == 0 || g_batch == 0) {
+            rc = zero_or_bias_fill(c, da, a_elems, 1, nullptr, acc_da);
+            if (rc) return rc;
+        } else {
+            int64_t ob[MNI_B200_MAX_DIMS];
+            const int onb = broadcast_shape(dc->shape, gn - 2, b->shape, b->ndim - 2, ob);
+            if (onb < 0) return fail(MNI_B200_ERR_BROADCAST, "dc and b batch shapes are not broadcastable");
+            Operand X, Y;
+            rc = make_operand(c, *dc, false, X);   // rows M, contraction N
+            if (rc) return rc;
+            rc = make_operand(c, *b, false, Y);    // rows K, contraction N
+            if (rc) return rc;
+            X.batch = g_batch;
+            Y.batch = s.b_batch;
+            rc = grad_gemm(c, X, Y, s.M, s.K, s.N, ob, onb, *a, da, acc_da);
+            if (rc) return rc;
+        }
+    }
+
+    // grad_b = unbroadcast(a^T . dc, b.shape)   (ops/matmul.rs:242-251)
+    if (db && b_elems > 0) {
+        if (s.M == 0 || g_batch == 0) {
+            rc = zero_or_bias_fill(c, db, b_elems, 1, nullptr, acc_db);
+            if (rc) return rc;
+        } else {
+            const bool want_skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
+                                     ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 16);
+            const bool plain2d = s.batch == 1 && g_batch == 1 && s.M <= 16;
+            if (want_skinny && plain2d && (a->stride[a->ndim - 1] == 1 || s.K == 1) &&
+                (dc->stride[gn - 1] == 1 || s.N == 1)) {
+                if (!c.dry()) {
+                    rc = launch_skinny_dw(a->ptr, a->stride[a->ndim - 2], dc->ptr, dc->stride[gn - 2], db, s.N, acc_db,
+                                          s.M, s.N, s.K, c.stream);
+                    if (rc) return rc;
+                }
+            } else {
+                int64_t ob[MNI_B200_MAX_DIMS];
+                const int onb = broadcast_shape(a->shape, a->ndim - 2, dc->shape, gn - 2, ob);
+                if (onb < 0) return fail(MNI_B200_ERR_BROADCAST, "a and dc batch shapes are not broadcastable");
+                Operand X, Y;
+                rc = make_operand(c, *a, true, X);     // rows K, contraction M
+                if (rc) return rc;
+                rc = make_operand(c, *dc, true, Y);    // rows N, contraction M
+                if (rc) return rc;
+                X.batch = s.a_batch;
+                Y.batch = g_batch;
+                rc = grad_gemm(c, X, Y, s.K, s.N, s.M, ob, onb, *b, db, acc_db);
+                if (rc) return rc;
+            }
+        }
+    }
+    return MNI_B200_OK;
+}
+
+// Runs `body` twice: a dry pass that sizes the scratch, then the real pass.
+template <class Body>
+int with_scratch(uint32_t flags, void *stream, Body body) {
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(st->mu);
+    Call dry;
+    dry.st = st; dry.arena.st = st; dry.arena.dry = true; dry.stream = static_cast<cudaStream_t>(stream); dry.flags = flags;
+    rc = body(dry);
+    if (rc) return rc;
+    Call real;
+    real.st = st; real.arena.st = st; real.arena.dry = false; real.stream = static_cast<cudaStream_t>(stream); real.flags = flags;
+    if (dry.arena.used > 0) {
+        rc = scratch_base(*st, dry.arena.used, &real.base);
+        if (rc) return rc;
+    }
+    return body(real);
+}
+
+}  // namespace
+
+int fail(int status, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof(t_error), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+}  // namespace mni
+
+using namespace mni;
+
+extern "C" {
+
+int mni_b200_version(void) { return 100; }
+
+const char *mni_b200_last_error(void) { return t_error; }
+
+uint64_t mni_b200_launch_count(void) { return g_launches.load(); }
+
+int mni_b200_matmul_fwd(const mni_b200_view *a, const mni_b200_view *b, float *c, const float *bias,
+                        uint32_t flags, void *stream) {
+    return with_scratch(flags, stream, [&](Call &call) { return fwd_body(call, a, b, c, bias); });
+}
+
+int mni_b200_matmul_bwd(const mni_b200_view *a, const mni_b200_view *b, const mni_b200_view *dc, float *da,
+                        float *db, float *dbias, uint32_t flags, void *stream) {
+    return with_scratch(flags, stream, [&](Call &call) { return bwd_body(call, a, b, dc, da, db, dbias); });
+}
+
+int mni_b200_add_bias(const float *y, const float *bias, float *out, int64_t rows, int64_t n, void *stream) {
+    if (rows < 0 || n < 0) return fail(MNI_B200_ERR_ARG, "negative extent");
+    if (rows * n == 0) return MNI_B200_OK;
+    if (!y || !bias || !out) return fail(MNI_B200_ERR_ARG, "null pointer");
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    return launch_add_bias(y, bias, out, rows, n, static_cast<cudaStream_t>(stream));
+}
+
+int mni_b200_add_bias_bwd(const float *dy, float *d_y, float *dbias, int64_t rows, int64_t n, uint32_t flags,
+                          void *stream) {
+    if (rows < 0 || n < 0) return fail(MNI_B200_ERR_ARG, "negative extent");
+    if (!dy && rows * n > 0) return fail(MNI_B200_ERR_ARG, "dy is null");
+    return with_scratch(flags, stream, [&](Call &c) -> int {
+        if (d_y && d_y != dy && !c.dry()) {
+            int rc = launch_copy(dy, d_y, rows * n, c.stream);
+            if (rc) return rc;
+        }
+        if (!dbias || n == 0) return MNI_B200_OK;
+        const bool acc = (flags & MNI_B200_ACCUMULATE_DBIAS) != 0;
+        if (rows == 0) return zero_or_bias_fill(c, dbias, 1, n, nullptr, acc);
+        const size_t poff = c.arena.reserve(colsum_partial_bytes(rows, n, c.st->sm_count));
+        if (c.dry()) return MNI_B200_OK;
+        return launch_colsum(dy, n, dbias, rows, n, acc, c.at(poff), c.st->sm_count, c.stream);
+    });
+}
+
+int mni_b200_contiguous(const mni_b200_view *src, float *dst, void *stream) {
+    int rc = check_view(src, "src", 1);
+    if (rc) return rc;
+    if (prod(src->shape, src->ndim) == 0) return MNI_B200_OK;
+    if (!dst) return fail(MNI_B200_ERR_ARG, "dst is null");
+    DeviceState *st = nullptr;
+    rc = device_state(&st);
+    if (rc) return rc;
+    return launch_pack(*src, dst, src->shape[src->ndim - 1], static_cast<cudaStream_t>(stream));
+}
+
+int mni_b200_workspace_set(void *ptr, size_t bytes) {
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(st->mu);
+    if (!ptr || bytes == 0) { st->user_ws = nullptr; st->user_bytes = 0; return MNI_B200_OK; }
+    if ((reinterpret_cast<uintptr_t>(ptr) & 255) != 0) return fail(MNI_B200_ERR_ARG, "scratch must be 256-byte aligned");
+    st->user_ws = static_cast<uint8_t *>(ptr);
+    st->user_bytes = bytes;
+    return MNI_B200_OK;
+}
+
+int mni_b200_workspace_query(const mni_b200_view *a, const mni_b200_view *b, uint32_t flags, size_t *bytes) {
+    if (!bytes) return fail(MNI_B200_ERR_ARG, "bytes is null");
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    Shapes s;
+    rc = analyse(a, b, s);
+    if (rc) return rc;
+    // The forward output's gradient: contiguous, broadcast batch + [M, N].
+    mni_b200_view dc{};
+    dc.ptr = reinterpret_cast<const float *>(static_cast<uintptr_t>(256));
+    dc.ndim = s.out_nb + 2;
+    for (int i = 0; i < s.out_nb; ++i) dc.shape[i] = s.out_batch[i];
+    dc.shape[s.out_nb] = s.M; dc.shape[s.out_nb + 1] = s.N;
+    int64_t acc = 1;
+    for (int d = dc.ndim - 1; d >= 0; --d) { dc.stride[d] = acc; acc *= dc.shape[d]; }
+    float *fake = reinterpret_cast<float *>(static_cast<uintptr_t>(256));
+    Call c1;
+    c1.st = st; c1.arena.dry = true; c1.stream = nullptr; c1.flags = flags;
+    rc = fwd_body(c1, a, b, fake, nullptr);
+    if (rc) return rc;
+    Call c2;
+    c2.st = st; c2.arena.dry = true; c2.stream = nullptr; c2.flags = flags;
+    rc = bwd_body(c2, a, b, &dc, fake, fake, fake);
+    if (rc) return rc;
+    *bytes = std::max(c1.arena.used, c2.arena.used);
+    return MNI_B200_OK;
+}
+
+int mni_b200_device_status(void *stream, uint32_t *detail) {
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    MNI_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    unsigned int word = 0;
+    MNI_CUDA(cudaMemcpy(&word, st->err_word, sizeof(word), cudaMemcpyDeviceToHost));
+    if (detail) *detail = word;
+    if (word != 0) {
+        MNI_CUDA(cudaMemset(st->err_word, 0, sizeof(word)));
+        return fail(MNI_B200_ERR_TIMEOUT, "a kernel gave up on a bounded wait (code 0x%x: role %u, slot %u)", word,
+                    word >> 8, word & 0xffu);
+    }
+    return MNI_B200_OK;
+}
+
+int mni_b200_release(void) {
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(st->mu);
+    if (st->ws) {
+        MNI_CUDA(cudaDeviceSynchronize());
+        MNI_CUDA(cudaFree(st->ws));
+        st->ws = nullptr;
+        st->ws_bytes = 0;
+    }
+    return MNI_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,109 @@
+// Internal interfaces between the C-ABI host logic (api.cu) and the kernel
+// launchers.  Nothing here is exported.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <string>
+
+#include "mni_b200.h"
+
+namespace mni {
+
+// ---------------------------------------------------------------------------
+// error plumbing
+// ---------------------------------------------------------------------------
+int fail(int status, const char *fmt, ...);          // records the thread-local message, returns status
+extern std::atomic<uint64_t> g_launches;              // kernels launched by this library
+
+#define MNI_CUDA(call)                                                                   \
+    do {                                                                                 \
+        cudaError_t e__ = (call);                                                        \
+        if (e__ != cudaSuccess)                                                          \
+            return ::mni::fail(MNI_B200_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e__)); \
+    } while (0)
+
+#define MNI_LAUNCH_CHECK(name)                                                           \
+    do {                                                                                 \
+        ::mni::g_launches.fetch_add(1, std::memory_order_relaxed);                       \
+        cudaError_t e__ = cudaGetLastError();                                            \
+        if (e__ != cudaSuccess)                                                          \
+            return ::mni::fail(MNI_B200_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e__)); \
+    } while (0)
+
+// ---------------------------------------------------------------------------
+// One GEMM operand as the tensor-core kernel reads it through a TMA descriptor.
+// "rows" is the operand's non-contraction extent (M for A, N for B), "kdim" the
+// contraction extent of one batch.  Exactly one of the two matrix dims has unit
+// stride: k_major says which.
+// ---------------------------------------------------------------------------
+struct Operand {
+    const float *ptr = nullptr;
+    bool k_major = true;
+    int64_t rows = 0, kdim = 0;
+    int64_t ld = 0;                // element stride of the non-unit matrix dim
+    int64_t bshape[3] = {1, 1, 1}; // operand batch dims, outermost first (front-padded with 1)
+    int64_t bstride[3] = {0, 0, 0};
+    int64_t batch = 1;             // product of bshape
+};
+
+struct GemmProblem {
+    Operand A, B;                  // C[M,N] = sum_k A[m,k] * B[n,k]
+    int64_t M = 0, N = 0, K = 0;
+    int64_t batch = 1;             // output batches
+    int64_t fold = 1;              // batches summed inside the contraction (weight-gradient reduce)
+    float *C = nullptr;
+    int64_t ldc = 0, c_bstride = 0;
+    const float *bias = nullptr;   // per output column, may be null
+    bool accumulate = false;       // C += ...
+    bool fast_tf32 = false;        // one TF32 pass instead of the 3-pass split
+    int force_splits = 0;          // tests
+};
+
+// Scratch layout handed to launchers (all device memory, owned by api.cu).
+struct Scratch {
+    uint8_t *base = nullptr;
+    size_t bytes = 0;
+    uint32_t *err_word = nullptr;  // device-side timeout record (inside base)
+};
+
+// Bytes of split-K partial storage launch_gemm_tc would use for this problem (0 if none).
+size_t gemm_tc_partial_bytes(const GemmProblem &p, int sm_count);
+
+// Tensor-core path: TMA -> smem -> (hi/lo split) -> tcgen05.mma -> TMEM -> global.
+// `partial` must hold gemm_tc_partial_bytes() bytes when that is non-zero.
+int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int sm_count,
+                   cudaStream_t stream);
+
+// Skinny path (few output rows, HBM-bound): CUDA-core fp32 FMA kernels.
+//   y[M,N] = x[M,K] . W[K,N]          (W row-major, ldw)           M <= 16
+bool skinny_fwd_supported(int64_t M, int64_t N, int64_t K);
+size_t skinny_fwd_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count);
+int launch_skinny_fwd(const float *x, int64_t ldx, const float *W, int64_t ldw, float *y, int64_t ldy,
+                      const float *bias, bool accumulate, int64_t M, int64_t N, int64_t K,
+                      float *partial, int sm_count, cudaStream_t stream);
+//   dx[M,K] = dy[M,N] . W[K,N]^T                                    M <= 16
+int launch_skinny_dx(const float *dy, int64_t lddy, const float *W, int64_t ldw, float *dx, int64_t lddx,
+                     bool accumulate, int64_t M, int64_t N, int64_t K, cudaStream_t stream);
+//   dW[K,N] = x[M,K]^T . dy[M,N]                                     M <= 16
+int launch_skinny_dw(const float *x, int64_t ldx, const float *dy, int64_t lddy, float *dW, int64_t lddw,
+                     bool accumulate, int64_t M, int64_t N, int64_t K, cudaStream_t stream);
+
+// Pointwise / reduction helpers.
+int launch_add_bias(const float *y, const float *bias, float *out, int64_t rows, int64_t n,
+                    cudaStream_t stream);
+size_t colsum_partial_bytes(int64_t rows, int64_t n, int sm_count);
+int launch_colsum(const float *dy, int64_t ld, float *out, int64_t rows, int64_t n, bool accumulate,
+                  float *partial, int sm_count, cudaStream_t stream);
+int launch_copy(const float *src, float *dst, int64_t n, cudaStream_t stream);
+// dst[row-major, ld_dst on the last dim] = gather of a strided view
+int launch_pack(const mni_b200_view &src, float *dst, int64_t ld_dst, cudaStream_t stream);
+// device-side utils::unbroadcast: out[orig] (+)= sum over broadcast dims of grad[gshape]
+int launch_unbroadcast(const float *grad, const int64_t *gshape, int gnd, const int64_t *oshape, int ond,
+                       float *out, bool accumulate, cudaStream_t stream);
+
+}  // namespace mni

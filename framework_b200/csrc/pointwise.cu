@@ -1,0 +1,250 @@
+// HBM-bound helpers around the GEMM: bias add, column sums (dbias), device-side
+// gather of strided views, device-side unbroadcast, plain copy.
+#include "internal.h"
+
+#include <algorithm>
+
+namespace mni {
+
+namespace {
+
+constexpr int kMaxDims = MNI_B200_MAX_DIMS;
+
+int grid_for(long long work_items, int threads, int sm_count_hint = 148) {
+    const long long blocks = (work_items + threads - 1) / threads;
+    return static_cast<int>(std::max<long long>(1, std::min<long long>(blocks, sm_count_hint * 16LL)));
+}
+
+// out[r, j] = y[r, j] + bias[j]; one float4 per thread-iteration when n % 4 == 0.
+__global__ void add_bias_vec_kernel(const float4 *__restrict__ y, const float4 *__restrict__ bias,
+                                    float4 *__restrict__ out, long long total4, int n4) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total4;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const float4 b = __ldg(bias + static_cast<int>(i % n4));
+        float4 v = y[i];
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+        out[i] = v;
+    }
+}
+__global__ void add_bias_scalar_kernel(const float *__restrict__ y, const float *__restrict__ bias,
+                                       float *__restrict__ out, long long total, long long n) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        out[i] = y[i] + __ldg(bias + i % n);
+}
+
+// Column sums, stage 1: block (bx, by) sums rows [by*rows_per, ...) of a 128-column strip
+// (32 lanes x float4).  8 warps take interleaved rows and are combined through shared
+// memory in a fixed order, so the result does not depend on scheduling.
+__global__ void colsum_partial_kernel(const float *__restrict__ dy, long long ld, float *__restrict__ partial,
+                                      long long rows, long long n, long long rows_per) {
+    __shared__ float4 red[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long col = (static_cast<long long>(blockIdx.x) * 32 + lane) * 4;
+    const long long r0 = blockIdx.y * rows_per;
+    const long long r1 = min(rows, r0 + rows_per);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const bool vec = ((ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(dy) & 15) == 0) && col + 3 < n;
+    if (col < n) {
+        for (long long r = r0 + warp; r < r1; r += 8) {
+            const float *p = dy + r * ld + col;
+            if (vec) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(p));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            } else {
+                acc.x += __ldg(p);
+                if (col + 1 < n) acc.y += __ldg(p + 1);
+                if (col + 2 < n) acc.z += __ldg(p + 2);
+                if (col + 3 < n) acc.w += __ldg(p + 3);
+            }
+        }
+    }
+    red[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && col < n) {
+        float4 s = red[0][lane];
+        for (int w = 1; w < 8; ++w) {
+            s.x += red[w][lane].x; s.y += red[w][lane].y; s.z += red[w][lane].z; s.w += red[w][lane].w;
+        }
+        float *o = partial + static_cast<long long>(blockIdx.y) * n + col;
+        o[0] = s.x;
+        if (col + 1 < n) o[1] = s.y;
+        if (col + 2 < n) o[2] = s.z;
+        if (col + 3 < n) o[3] = s.w;
+    }
+}
+// stage 2: out[j] (+)= sum over slabs, ascending.
+__global__ void colsum_final_kernel(const float *__restrict__ partial, float *__restrict__ out, long long n,
+                                    int slabs, int accumulate) {
+    const long long j = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (j >= n) return;
+    float s = partial[j];
+    for (int i = 1; i < slabs; ++i) s += partial[static_cast<long long>(i) * n + j];
+    out[j] = accumulate ? out[j] + s : s;
+}
+
+struct PackArgs {
+    int nd;
+    long long shape[kMaxDims];
+    long long stride[kMaxDims];
+    long long ld_dst;      // destination pitch of the last dim's rows
+    long long total;
+};
+// dst row-major (last dim padded to ld_dst) <- strided view.  Threads run along the
+// destination, so writes are coalesced; reads are as coalesced as the view allows.
+__global__ void pack_kernel(const float *__restrict__ src, float *__restrict__ dst, const PackArgs a) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < a.total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        long long rem = i, off = 0;
+        const long long last = a.shape[a.nd - 1];
+        const long long c = rem % last;
+        rem /= last;
+        off += c * a.stride[a.nd - 1];
+        const long long row = rem;
+        for (int d = a.nd - 2; d >= 0; --d) {
+            const long long q = rem % a.shape[d];
+            rem /= a.shape[d];
+            off += q * a.stride[d];
+        }
+        dst[row * a.ld_dst + c] = src[off];
+    }
+}
+
+struct UnbArgs {
+    int nd;                      // dims of the original (small) shape, right-aligned into the grad shape
+    long long oshape[kMaxDims];  // original shape
+    long long gstride[kMaxDims]; // grad stride of the matching grad dim
+    int nred;                    // number of reduced (broadcast) dims incl. leading extra dims
+    long long rshape[kMaxDims];  // extents of reduced dims, outermost first
+    long long rstride[kMaxDims]; // grad strides of reduced dims
+    long long rtotal;
+    long long total;
+};
+// One thread per element of the original shape; it sums the grad elements that
+// broadcast onto it in ascending flat order -- the order utils::unbroadcast adds them.
+__global__ void unbroadcast_kernel(const float *__restrict__ grad, float *__restrict__ out, const UnbArgs a,
+                                   int accumulate) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < a.total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        long long rem = i, base = 0;
+        for (int d = a.nd - 1; d >= 0; --d) {
+            const long long q = rem % a.oshape[d];
+            rem /= a.oshape[d];
+            base += q * a.gstride[d];
+        }
+        float s = 0.f;
+        for (long long r = 0; r < a.rtotal; ++r) {
+            long long rr = r, off = base;
+            for (int d = a.nred - 1; d >= 0; --d) {
+                off += (rr % a.rshape[d]) * a.rstride[d];
+                rr /= a.rshape[d];
+            }
+            s += grad[off];
+        }
+        out[i] = accumulate ? out[i] + s : s;
+    }
+}
+
+}  // namespace
+
+int launch_add_bias(const float *y, const float *bias, float *out, int64_t rows, int64_t n,
+                    cudaStream_t stream) {
+    const long long total = static_cast<long long>(rows) * n;
+    if (total == 0) return MNI_B200_OK;
+    const bool vec = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out) |
+                                       reinterpret_cast<uintptr_t>(bias)) & 15) == 0;
+    if (vec) {
+        add_bias_vec_kernel<<<grid_for(total / 4, 256), 256, 0, stream>>>(
+            reinterpret_cast<const float4 *>(y), reinterpret_cast<const float4 *>(bias),
+            reinterpret_cast<float4 *>(out), total / 4, static_cast<int>(n / 4));
+    } else {
+        add_bias_scalar_kernel<<<grid_for(total, 256), 256, 0, stream>>>(y, bias, out, total, n);
+    }
+    MNI_LAUNCH_CHECK("add_bias");
+    return MNI_B200_OK;
+}
+
+static int colsum_slabs(int64_t rows, int64_t n, int sm_count) {
+    const long long strips = (n + 127) / 128;
+    long long slabs = std::max<long long>(1, (sm_count * 4LL) / strips);
+    slabs = std::min<long long>(slabs, (rows + 63) / 64);
+    return static_cast<int>(std::max<long long>(1, slabs));
+}
+
+size_t colsum_partial_bytes(int64_t rows, int64_t n, int sm_count) {
+    return static_cast<size_t>(colsum_slabs(rows, n, sm_count)) * n * sizeof(float);
+}
+
+int launch_colsum(const float *dy, int64_t ld, float *out, int64_t rows, int64_t n, bool accumulate,
+                  float *partial, int sm_count, cudaStream_t stream) {
+    if (n == 0) return MNI_B200_OK;
+    const int slabs = colsum_slabs(rows, n, sm_count);
+    const long long rows_per = (rows + slabs - 1) / slabs;
+    dim3 grid(static_cast<unsigned>((n + 127) / 128), static_cast<unsigned>(slabs));
+    colsum_partial_kernel<<<grid, 256, 0, stream>>>(dy, ld, partial, rows, n, rows_per);
+    MNI_LAUNCH_CHECK("colsum_partial_kernel");
+    colsum_final_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(partial, out, n, slabs,
+                                                                                  accumulate ? 1 : 0);
+    MNI_LAUNCH_CHECK("colsum_final_kernel");
+    return MNI_B200_OK;
+}
+
+int launch_copy(const float *src, float *dst, int64_t n, cudaStream_t stream) {
+    if (n == 0 || src == dst) return MNI_B200_OK;
+    MNI_CUDA(cudaMemcpyAsync(dst, src, static_cast<size_t>(n) * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+    return MNI_B200_OK;
+}
+
+int launch_pack(const mni_b200_view &src, float *dst, int64_t ld_dst, cudaStream_t stream) {
+    PackArgs a{};
+    a.nd = src.ndim;
+    a.total = 1;
+    for (int d = 0; d < src.ndim; ++d) {
+        a.shape[d] = src.shape[d];
+        a.stride[d] = src.stride[d];
+        a.total *= src.shape[d];
+    }
+    a.ld_dst = ld_dst;
+    if (a.total == 0) return MNI_B200_OK;
+    pack_kernel<<<grid_for(a.total, 256), 256, 0, stream>>>(src.ptr, dst, a);
+    MNI_LAUNCH_CHECK("pack_kernel");
+    return MNI_B200_OK;
+}
+
+int launch_unbroadcast(const float *grad, const int64_t *gshape, int gnd, const int64_t *oshape, int ond,
+                       float *out, bool accumulate, cudaStream_t stream) {
+    long long gstr[kMaxDims];
+    long long acc = 1;
+    for (int d = gnd - 1; d >= 0; --d) { gstr[d] = acc; acc *= gshape[d]; }
+    UnbArgs a{};
+    a.nd = ond;
+    a.total = 1;
+    a.rtotal = 1;
+    a.nred = 0;
+    const int off = gnd - ond;
+    for (int d = 0; d < off; ++d) {           // leading dims the original does not have
+        a.rshape[a.nred] = gshape[d];
+        a.rstride[a.nred] = gstr[d];
+        a.rtotal *= gshape[d];
+        ++a.nred;
+    }
+    for (int d = 0; d < ond; ++d) {
+        a.oshape[d] = oshape[d];
+        a.total *= oshape[d];
+        if (oshape[d] == 1 && gshape[d + off] != 1) {
+            a.gstride[d] = 0;
+            a.rshape[a.nred] = gshape[d + off];
+            a.rstride[a.nred] = gstr[d + off];
+            a.rtotal *= gshape[d + off];
+            ++a.nred;
+        } else {
+            a.gstride[d] = gstr[d + off];
+        }
+    }
+    if (a.total == 0) return MNI_B200_OK;
+    unbroadcast_kernel<<<grid_for(a.total, 256), 256, 0, stream>>>(grad, out, a, accumulate ? 1 : 0);
+    MNI_LAUNCH_CHECK("unbroadcast_kernel");
+    return MNI_B200_OK;
+}
+
+}  // namespace mni

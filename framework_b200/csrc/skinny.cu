@@ -1,0 +1,231 @@
+// Skinny path: at most 16 output rows (decode-like M).  These shapes move the whole
+// weight matrix through the SMs for a handful of flops per byte, so they are bound by
+// HBM, not by the tensor pipe; they run as CUDA-core fp32 FMA kernels with 16-byte
+// loads and a split of the contraction over the grid.
+//
+//   fwd : y[M,N]  = x[M,K] . W[K,N] (+bias)        W streamed once, split-K partials
+//   dW  : dW[K,N] = x[M,K]^T . dy[M,N]             dW written once
+// (dx = dy . W^T is a K-major/K-major product and goes through the tensor-core kernel.)
+#include "internal.h"
+
+#include <algorithm>
+
+namespace mni {
+
+namespace {
+
+constexpr int kSkinnyThreads = 128;   // each thread owns 4 consecutive output columns
+
+// grid = (n strips of 512 columns, k splits).  x[M, k-slice] is staged in shared memory.
+template <int MT>
+__global__ void __launch_bounds__(kSkinnyThreads)
+skinny_fwd_kernel(const float *__restrict__ x, long long ldx, const float *__restrict__ W, long long ldw,
+                  float *__restrict__ partial, int M, long long N, long long K, long long k_per) {
+    extern __shared__ float xs[];   // [MT][k_per]
+    const long long k0 = blockIdx.y * k_per;
+    const long long k1 = min(K, k0 + k_per);
+    const int kc = static_cast<int>(k1 - k0);
+    for (int i = threadIdx.x; i < MT * static_cast<int>(k_per); i += kSkinnyThreads) {
+        const int m = i / static_cast<int>(k_per), kk = i - m * static_cast<int>(k_per);
+        xs[i] = (m < M && kk < kc) ? __ldg(x + m * ldx + k0 + kk) : 0.f;
+    }
+    __syncthreads();
+    const long long col = (static_cast<long long>(blockIdx.x) * kSkinnyThreads + threadIdx.x) * 4;
+    if (col >= N) return;
+    const bool vec = col + 3 < N;
+    float4 acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float *wp = W + k0 * ldw + col;
+    int kk = 0;
+    if (vec) {
+        for (; kk + 4 <= kc; kk += 4) {
+            float4 w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) w[u] = __ldcs(reinterpret_cast<const float4 *>(wp + (kk + u) * ldw));
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const float4 xv = *reinterpret_cast<const float4 *>(xs + m * k_per + kk);
+                const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    acc[m].x = fmaf(xa[u], w[u].x, acc[m].x);
+                    acc[m].y = fmaf(xa[u], w[u].y, acc[m].y);
+                    acc[m].z = fmaf(xa[u], w[u].z, acc[m].z);
+                    acc[m].w = fmaf(xa[u], w[u].w, acc[m].w);
+                }
+            }
+        }
+    }
+    for (; kk < kc; ++kk) {
+        float w[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int e = 0; e < 4; ++e)
+            if (col + e < N) w[e] = __ldg(wp + kk * ldw + e);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const float xv = xs[m * k_per + kk];
+            acc[m].x = fmaf(xv, w[0], acc[m].x);
+            acc[m].y = fmaf(xv, w[1], acc[m].y);
+            acc[m].z = fmaf(xv, w[2], acc[m].z);
+            acc[m].w = fmaf(xv, w[3], acc[m].w);
+        }
+    }
+    float *out = partial + static_cast<long long>(blockIdx.y) * M * N;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        if (m >= M) break;
+        float *o = out + m * N + col;
+        const float a[4] = {acc[m].x, acc[m].y, acc[m].z, acc[m].w};
+        for (int e = 0; e < 4; ++e)
+            if (col + e < N) o[e] = a[e];
+    }
+}
+
+// y[m, j] = sum over splits (ascending) (+ bias[j]) (+ y[m, j])
+__global__ void skinny_reduce_kernel(const float *__restrict__ partial, float *__restrict__ y, long long ldy,
+                                     const float *__restrict__ bias, int accumulate, int splits, int M,
+                                     long long N) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= M * N) return;
+    const long long j = i % N;
+    const int m = static_cast<int>(i / N);
+    float s = partial[i];
+    for (int sp = 1; sp < splits; ++sp) s += partial[static_cast<long long>(sp) * M * N + i];
+    if (bias) s += __ldg(bias + j);
+    float *dst = y + m * ldy + j;
+    *dst = accumulate ? *dst + s : s;
+}
+
+// grid = (n strips of 512 columns, k slabs).  dy[M, 4 cols] lives in registers; each
+// k row of dW is one float4 store per thread.
+template <int MT>
+__global__ void __launch_bounds__(kSkinnyThreads)
+skinny_dw_kernel(const float *__restrict__ x, long long ldx, const float *__restrict__ dy, long long lddy,
+                 float *__restrict__ dW, long long lddw, int accumulate, int M, long long N, long long K,
+                 long long k_per) {
+    extern __shared__ float xs[];   // [k_per][MT]
+    const long long k0 = blockIdx.y * k_per;
+    const long long k1 = min(K, k0 + k_per);
+    const int kc = static_cast<int>(k1 - k0);
+    for (int i = threadIdx.x; i < MT * kc; i += kSkinnyThreads) {
+        const int kk = i % kc, m = i / kc;
+        xs[kk * MT + m] = m < M ? __ldg(x + m * ldx + k0 + kk) : 0.f;
+    }
+    __syncthreads();
+    const long long col = (static_cast<long long>(blockIdx.x) * kSkinnyThreads + threadIdx.x) * 4;
+    if (col >= N) return;
+    float g[MT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+        for (int e = 0; e < 4; ++e) g[m][e] = (m < M && col + e < N) ? __ldg(dy + m * lddy + col + e) : 0.f;
+    const bool vec = (col + 3 < N) && ((lddw & 3) == 0) && ((reinterpret_cast<uintptr_t>(dW) & 15) == 0);
+    for (int kk = 0; kk < kc; ++kk) {
+        float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const float xv = xs[kk * MT + m];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = fmaf(xv, g[m][e], o[e]);
+        }
+        float *dst = dW + (k0 + kk) * lddw + col;
+        if (vec) {
+            float4 v = make_float4(o[0], o[1], o[2], o[3]);
+            if (accumulate) {
+                const float4 old = *reinterpret_cast<const float4 *>(dst);
+                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+            }
+            __stcs(reinterpret_cast<float4 *>(dst), v);
+        } else {
+            for (int e = 0; e < 4; ++e)
+                if (col + e < N) dst[e] = accumulate ? dst[e] + o[e] : o[e];
+        }
+    }
+}
+
+int pick_mt(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16; }
+
+struct FwdPlan { int splits; long long k_per; int strips; };
+
+FwdPlan fwd_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
+    FwdPlan pl;
+    pl.strips = static_cast<int>((N + 4 * kSkinnyThreads - 1) / (4 * kSkinnyThreads));
+    // Enough blocks to fill the GPU a few times over, but keep the partial traffic
+    // (splits * M * N * 8 bytes) well under the weight traffic (K * N * 4 bytes).
+    long long want = std::max<long long>(1, (sm_count * 4LL) / pl.strips);
+    long long cap = std::max<long long>(1, K / (16 * std::max<int64_t>(M, 1)));
+    long long splits = std::min(want, cap);
+    splits = std::min<long long>(splits, (K + 15) / 16);
+    splits = std::max<long long>(splits, (K + 2047) / 2048);   // shared-memory bound on a k slice
+    pl.k_per = ((K + splits - 1) / splits + 3) & ~3LL;
+    pl.splits = static_cast<int>((K + pl.k_per - 1) / pl.k_per);
+    return pl;
+}
+
+}  // namespace
+
+bool skinny_fwd_supported(int64_t M, int64_t N, int64_t K) {
+    return M >= 1 && M <= 16 && N >= 1 && K >= 1;
+}
+
+size_t skinny_fwd_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count) {
+    const FwdPlan pl = fwd_plan(M, N, K, sm_count);
+    return static_cast<size_t>(pl.splits) * M * N * sizeof(float);
+}
+
+int launch_skinny_fwd(const float *x, int64_t ldx, const float *W, int64_t ldw, float *y, int64_t ldy,
+                      const float *bias, bool accumulate, int64_t M, int64_t N, int64_t K, float *partial,
+                      int sm_count, cudaStream_t stream) {
+    const FwdPlan pl = fwd_plan(M, N, K, sm_count);
+    const int mt = pick_mt(M);
+    dim3 grid(pl.strips, pl.splits);
+    const size_t smem = static_cast<size_t>(mt) * pl.k_per * sizeof(float);
+    const bool vec_w = (ldw % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
+    if (!vec_w) return fail(MNI_B200_ERR_ARG, "skinny path needs a 16-byte aligned weight with ld %% 4 == 0");
+#define MNI_SKINNY_FWD(MT)                                                                             \
+    case MT:                                                                                           \
+        cudaFuncSetAttribute(skinny_fwd_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
+        skinny_fwd_kernel<MT><<<grid, kSkinnyThreads, smem, stream>>>(x, ldx, W, ldw, partial, (int)M, N, K, \
+                                                                      pl.k_per);                       \
+        break;
+    switch (mt) {
+        MNI_SKINNY_FWD(1) MNI_SKINNY_FWD(2) MNI_SKINNY_FWD(4) MNI_SKINNY_FWD(8) MNI_SKINNY_FWD(16)
+    }
+#undef MNI_SKINNY_FWD
+    MNI_LAUNCH_CHECK("skinny_fwd_kernel");
+    const long long total = M * N;
+    skinny_reduce_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+        partial, y, ldy, bias, accumulate ? 1 : 0, pl.splits, static_cast<int>(M), N);
+    MNI_LAUNCH_CHECK("skinny_reduce_kernel");
+    return MNI_B200_OK;
+}
+
+int launch_skinny_dx(const float *, int64_t, const float *, int64_t, float *, int64_t, bool, int64_t, int64_t,
+                     int64_t, cudaStream_t) {
+    return fail(MNI_B200_ERR_ARG, "skinny dx runs on the tensor-core path");
+}
+
+int launch_skinny_dw(const float *x, int64_t ldx, const float *dy, int64_t lddy, float *dW, int64_t lddw,
+                     bool accumulate, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+    const int mt = pick_mt(M);
+    const int strips = static_cast<int>((N + 4 * kSkinnyThreads - 1) / (4 * kSkinnyThreads));
+    long long slabs = std::max<long long>(1, (148 * 8LL) / strips);
+    long long k_per = std::max<long long>(8, (K + slabs - 1) / slabs);
+    k_per = std::min<long long>(k_per, 1024);
+    slabs = (K + k_per - 1) / k_per;
+    dim3 grid(strips, static_cast<unsigned>(slabs));
+    const size_t smem = static_cast<size_t>(mt) * k_per * sizeof(float);
+#define MNI_SKINNY_DW(MT)                                                                              \
+    case MT:                                                                                           \
+        cudaFuncSetAttribute(skinny_dw_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
+        skinny_dw_kernel<MT><<<grid, kSkinnyThreads, smem, stream>>>(x, ldx, dy, lddy, dW, lddw,       \
+                                                                     accumulate ? 1 : 0, (int)M, N, K, k_per); \
+        break;
+    switch (mt) {
+        MNI_SKINNY_DW(1) MNI_SKINNY_DW(2) MNI_SKINNY_DW(4) MNI_SKINNY_DW(8) MNI_SKINNY_DW(16)
+    }
+#undef MNI_SKINNY_DW
+    MNI_LAUNCH_CHECK("skinny_dw_kernel");
+    return MNI_B200_OK;
+}
+
+}  // namespace mni

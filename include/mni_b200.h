@@ -1,0 +1,166 @@
+/*
+ * mni_b200.h -- C ABI of the sm_100a matmul library (libmni_b200.so).
+ *
+ * The library replaces the `#[cfg(feature = "cuda")]` bodies of the reference's
+ * matmul op and of the Linear bias add.  The reference keeps doing what it does
+ * today around the call: shape asserts, output allocation (`store.zeros`, whose
+ * buffers may hold stale data -- allocator.rs:61-66 -- so every output here is
+ * fully overwritten unless an ACCUMULATE flag is given) and `tape.record`.
+ *
+ * Conventions
+ *   - f32 only.  Pointers are device pointers on the CURRENT device; the
+ *     reference passes what GpuDevice::ptr / TensorStore::dev_ptr return
+ *     (device.rs:205-211, tensor.rs:359-362).
+ *   - `mni_b200_view` is what a GpuTensor carries: shape and strides in
+ *     ELEMENTS (tensor.rs:63-73).  Stride 0 is allowed on batch dims.
+ *   - All work is enqueued on `stream` (a cudaStream_t / CUstream passed as
+ *     void*; NULL = the legacy default stream, which is what cudarc's
+ *     default_stream() of device.rs:37 resolves to).  No call synchronises the
+ *     device except the ones documented to.
+ *   - Every function returns an mni_b200_status; mni_b200_last_error() gives the
+ *     message of the calling thread's last failure.  Nothing aborts or traps.
+ *   - Outputs are contiguous row-major in the logical shape the reference
+ *     expects (ops/matmul.rs:145, :211, :218).
+ *   - No cuBLAS, no CPU fallback: if the device is not sm_100 the calls fail
+ *     with MNI_B200_ERR_DEVICE.
+ */
+#ifndef MNI_B200_H
+#define MNI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MNI_B200_MAX_DIMS 8
+
+/* Exported symbols (the library is built with hidden default visibility). */
+#if defined(__GNUC__)
+#define MNI_B200_API __attribute__((visibility("default")))
+#else
+#define MNI_B200_API
+#endif
+
+typedef struct mni_b200_view {
+    const float *ptr;
+    int32_t ndim;                        /* 1..8 (matmul operands: 2..8)          */
+    int64_t shape[MNI_B200_MAX_DIMS];
+    int64_t stride[MNI_B200_MAX_DIMS];   /* elements                                */
+} mni_b200_view;
+
+typedef enum mni_b200_status {
+    MNI_B200_OK = 0,
+    MNI_B200_ERR_NDIM = 1,        /* "matmul requires at least 2D tensors" (ops/matmul.rs:89)      */
+    MNI_B200_ERR_INNER_DIM = 2,   /* "matmul inner dimensions must match"  (ops/matmul.rs:94)      */
+    MNI_B200_ERR_BROADCAST = 3,   /* batch dims not broadcastable (utils.rs:16)                     */
+    MNI_B200_ERR_ARG = 4,         /* null pointer, negative size, bad flag, shape mismatch          */
+    MNI_B200_ERR_DEVICE = 5,      /* no CUDA device / not compute capability 10.x                   */
+    MNI_B200_ERR_CUDA = 6,        /* a CUDA runtime/driver call failed (message has the detail)     */
+    MNI_B200_ERR_WORKSPACE = 7,   /* scratch memory could not be grown / caller's is too small      */
+    MNI_B200_ERR_TIMEOUT = 8,     /* a bounded device-side wait gave up (see mni_b200_device_status) */
+    MNI_B200_ERR_TOO_LARGE = 9    /* a dimension exceeds what the kernels index (2^31-1)            */
+} mni_b200_status;
+
+/* flags (OR together) */
+#define MNI_B200_PRECISION_3XTF32   0u        /* default: hi/lo split, 3 tensor-core passes, ~f32 accuracy  */
+#define MNI_B200_PRECISION_TF32     (1u << 0) /* fast mode: one TF32 pass                                   */
+#define MNI_B200_ACCUMULATE_C       (1u << 1) /* fwd: c  += a.b (+bias)   instead of overwrite              */
+#define MNI_B200_ACCUMULATE_DA      (1u << 2) /* bwd: da += ...                                             */
+#define MNI_B200_ACCUMULATE_DB      (1u << 3) /* bwd: db += ...                                             */
+#define MNI_B200_ACCUMULATE_DBIAS   (1u << 4) /* bwd: dbias += ...                                          */
+#define MNI_B200_FORCE_TENSOR_PATH  (1u << 8) /* tests: never take the skinny CUDA-core path                */
+#define MNI_B200_FORCE_SKINNY_PATH  (1u << 9) /* tests: take the skinny path whenever its kernel can run    */
+#define MNI_B200_FORCE_PACK         (1u << 10)/* tests: copy strided operands to scratch first              */
+#define MNI_B200_FORCE_SPLIT_K(s)   (((uint32_t)(s) & 0xffu) << 16) /* tests: split the contraction s ways  */
+
+/* Library version: major*10000 + minor*100 + patch. */
+MNI_B200_API int mni_b200_version(void);
+
+/* Message of the calling thread's most recent failing call ("" if none). */
+MNI_B200_API const char *mni_b200_last_error(void);
+
+/*
+ * Forward.  Replaces the cuBLAS gemm / gemm_strided_batched calls of
+ * ops/matmul.rs:145-190 and, for strided operands, the ensure_contiguous
+ * round trip of ops/matmul.rs:84-85 / tensor.rs:510-517.
+ *
+ *   c[batch..., M, N] = a[..., M, K] . b[..., K, N]  (+ bias[N] if bias != NULL)
+ *
+ * Batch dims broadcast as utils.rs:3-20; an operand whose flat batch count
+ * differs from the output's is indexed `batch % operand_batch` exactly as
+ * ops/matmul.rs:123-124 does.  `c` is contiguous.  A non-NULL `bias` fuses
+ * the Linear bias add (src/nn.ts:23-25) into the epilogue.
+ */
+MNI_B200_API int mni_b200_matmul_fwd(const mni_b200_view *a, const mni_b200_view *b, float *c,
+                        const float *bias, uint32_t flags, void *stream);
+
+/*
+ * Backward.  Replaces ops/matmul.rs:224-255: both transpose_last2 calls
+ * (:231, :242), both matmul_no_grad calls (:232, :243) and the device->host
+ * unbroadcast round trips (:234-240, :245-251).
+ *
+ *   da = unbroadcast(dc . b^T, a.shape)      db = unbroadcast(a^T . dc, b.shape)
+ *   dbias[N] = column sums of dc             (only if dbias != NULL)
+ *
+ * `dc` is the gradient of the forward output (shape = broadcast batch + [M,N],
+ * any strides).  da / db are contiguous in a's / b's logical shape; either may
+ * be NULL to skip it.  Transposes are never materialised; a gradient whose
+ * operand was broadcast over the batch is reduced inside the GEMM.
+ */
+MNI_B200_API int mni_b200_matmul_bwd(const mni_b200_view *a, const mni_b200_view *b, const mni_b200_view *dc,
+                        float *da, float *db, float *dbias, uint32_t flags, void *stream);
+
+/*
+ * Stand-alone bias add for the drop-in Linear path, where matmul and add are
+ * two separate N-API calls.  Replaces the add_bias_f32 launch of
+ * ops/elementwise.rs:105-130 (kernels/elementwise.cu:43-47):
+ *   out[r, j] = y[r, j] + bias[j],  r < rows, j < n.   out may alias y.
+ */
+MNI_B200_API int mni_b200_add_bias(const float *y, const float *bias, float *out, int64_t rows, int64_t n,
+                      void *stream);
+
+/*
+ * Backward of the bias add.  Replaces the device->host->device path of
+ * ops/elementwise.rs:224-229: d_y = copy of dy (skipped if d_y is NULL or
+ * equals dy), dbias[j] = sum over rows of dy[r, j].
+ */
+MNI_B200_API int mni_b200_add_bias_bwd(const float *dy, float *d_y, float *dbias, int64_t rows, int64_t n,
+                          uint32_t flags, void *stream);
+
+/*
+ * Device-side gather of a strided view into a contiguous row-major buffer.
+ * Replaces TensorStore::ensure_contiguous on the CUDA backend
+ * (tensor.rs:510-517, a device->host->device round trip in the reference).
+ */
+MNI_B200_API int mni_b200_contiguous(const mni_b200_view *src, float *dst, void *stream);
+
+/*
+ * Scratch memory.  By default the library owns one lazily grown buffer per
+ * device.  mni_b200_workspace_set hands it a caller-owned buffer instead
+ * (bytes == 0 / ptr == NULL returns to the library-owned one); calls then fail
+ * with MNI_B200_ERR_WORKSPACE rather than allocate.  mni_b200_workspace_query
+ * returns the bytes the given forward+backward problem may need.
+ */
+MNI_B200_API int mni_b200_workspace_set(void *ptr, size_t bytes);
+MNI_B200_API int mni_b200_workspace_query(const mni_b200_view *a, const mni_b200_view *b, uint32_t flags,
+                             size_t *bytes);
+
+/*
+ * Synchronises `stream` and reports whether any kernel of this library gave up
+ * on a bounded wait since the last call (MNI_B200_ERR_TIMEOUT, with the
+ * recorded role/stage word in *detail if detail != NULL).  Clears the record.
+ */
+MNI_B200_API int mni_b200_device_status(void *stream, uint32_t *detail);
+
+/* Number of kernels this library has launched in this process (all threads). */
+MNI_B200_API uint64_t mni_b200_launch_count(void);
+
+/* Releases the library-owned scratch of the current device (synchronises it). */
+MNI_B200_API int mni_b200_release(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MNI_B200_H */
