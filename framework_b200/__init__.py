@@ -1,0 +1,14 @@
+"""B200-native matmul hot path of mni-ml/framework: Tensor.matmul forward/backward and
+the Linear bias add, as hand-written sm_100a kernels behind a C ABI.
+
+``framework_b200.csrc`` holds the CUDA sources and the C ABI implementation,
+``framework_b200.ops`` the host-side mirror of the reference's operator interface.
+"""
+from . import _lib  # noqa: F401
+from .ops import (  # noqa: F401
+    Linear, add, add_backward, broadcast_shape, device_status, launch_count, matmul, matmul_backward,
+)
+from .tensor import DeviceTensor  # noqa: F401
+
+__all__ = ["DeviceTensor", "Linear", "add", "add_backward", "broadcast_shape", "device_status",
+           "launch_count", "matmul", "matmul_backward"]

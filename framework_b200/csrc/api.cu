@@ -521,11 +521,23 @@ uint64_t mni_b200_launch_count(void) { return g_launches.load(); }
 
 int mni_b200_matmul_fwd(const mni_b200_view *a, const mni_b200_view *b, float *c, const float *bias,
                         uint32_t flags, void *stream) {
+    Shapes s;   // argument errors are reported before any device is touched
+    int rc = analyse(a, b, s);
+    if (rc) return rc;
     return with_scratch(flags, stream, [&](Call &call) { return fwd_body(call, a, b, c, bias); });
 }
 
 int mni_b200_matmul_bwd(const mni_b200_view *a, const mni_b200_view *b, const mni_b200_view *dc, float *da,
                         float *db, float *dbias, uint32_t flags, void *stream) {
+    Shapes s;
+    int rc = analyse(a, b, s);
+    if (rc) return rc;
+    rc = check_view(dc, "dc", 2);
+    if (rc) return rc;
+    if (dc->shape[dc->ndim - 2] != s.M || dc->shape[dc->ndim - 1] != s.N)
+        return fail(MNI_B200_ERR_ARG, "dc is [.., %lld, %lld] but the forward output is [.., %lld, %lld]",
+                    (long long)dc->shape[dc->ndim - 2], (long long)dc->shape[dc->ndim - 1], (long long)s.M,
+                    (long long)s.N);
     return with_scratch(flags, stream, [&](Call &call) { return bwd_body(call, a, b, dc, da, db, dbias); });
 }
 

@@ -502,6 +502,11 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+int env_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
 int make_map(CUtensorMap *map, const Operand &op, int box_rows, int bk) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(MNI_B200_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
@@ -521,7 +526,10 @@ int make_map(CUtensorMap *map, const Operand &op, int box_rows, int bk) {
         dims[1] = static_cast<cuuint64_t>(op.kdim);
         box[0] = 32;
         box[1] = static_cast<cuuint32_t>(bk);
-        swz = CU_TENSOR_MAP_SWIZZLE_128B;
+        // 32-bit elements read MN-major by the tensor core use the 128-byte swizzle whose unit
+        // is a 32-byte chunk (8 k-steps' worth of one row pair), not the usual 16-byte chunk.
+        swz = static_cast<CUtensorMapSwizzle>(env_int("MNI_B200_DEBUG_MN_TMA_SWIZZLE",
+                                                      static_cast<int>(CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)));
     }
     // A size-1 dim never advances, but its stride must still be a positive multiple of 16 bytes.
     uint64_t span = 16;
@@ -553,11 +561,6 @@ struct Plan {
     int bn, bk, stages, splits, tiles_m, tiles_n, grid;
     size_t smem;
 };
-
-int env_int(const char *name, int dflt) {
-    const char *v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
 
 Plan make_plan(const GemmProblem &p, int sm_count) {
     Plan pl;
@@ -657,15 +660,17 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     k.b_bytes = static_cast<uint32_t>(pl.bn * pl.bk * 4);
     k.stage_bytes = (k.a_bytes + k.b_bytes) * (p.fast_tf32 ? 1u : 2u);
     // K-major tile: rows of BK floats, 8-row groups SBO apart, swizzle span = one row.
-    // MN-major tile: 32-float chunks of BK k-rows (LBO apart), 8 k-rows per swizzle atom (SBO = 1024).
+    // MN-major tile: 32-float chunks of BK k-rows (LBO apart); the 32-byte-unit swizzle repeats every
+    // 4 k-rows (SBO = 512), and one 8-deep k-step spans two such groups (1024 bytes).
     const uint32_t k_layout = pl.bk == 32 ? 2u : 4u;   // SWIZZLE_128B : SWIZZLE_64B
     const uint32_t k_sbo = static_cast<uint32_t>(8 * pl.bk * 4);
     const uint32_t mn_lbo = static_cast<uint32_t>(env_int("MNI_B200_DEBUG_MN_LBO", pl.bk * 128));
-    const uint32_t mn_sbo = static_cast<uint32_t>(env_int("MNI_B200_DEBUG_MN_SBO", 1024));
+    const uint32_t mn_sbo = static_cast<uint32_t>(env_int("MNI_B200_DEBUG_MN_SBO", 512));
+    const uint32_t mn_layout = static_cast<uint32_t>(env_int("MNI_B200_DEBUG_MN_LAYOUT", 1));   // SWIZZLE_128B_BASE32B
     if (p.A.k_major) { k.a_desc_hi = desc_hi_bits(k_sbo, k_layout); k.a_desc_lbo = 0; k.a_kstep = 2; }
-    else { k.a_desc_hi = desc_hi_bits(mn_sbo, 2u); k.a_desc_lbo = ((mn_lbo >> 4) & 0x3FFFu) << 16; k.a_kstep = 64; }
+    else { k.a_desc_hi = desc_hi_bits(mn_sbo, mn_layout); k.a_desc_lbo = ((mn_lbo >> 4) & 0x3FFFu) << 16; k.a_kstep = 64; }
     if (p.B.k_major) { k.b_desc_hi = desc_hi_bits(k_sbo, k_layout); k.b_desc_lbo = 0; k.b_kstep = 2; }
-    else { k.b_desc_hi = desc_hi_bits(mn_sbo, 2u); k.b_desc_lbo = ((mn_lbo >> 4) & 0x3FFFu) << 16; k.b_kstep = 64; }
+    else { k.b_desc_hi = desc_hi_bits(mn_sbo, mn_layout); k.b_desc_lbo = ((mn_lbo >> 4) & 0x3FFFu) << 16; k.b_kstep = 64; }
     k.C = p.C;
     k.ldc = p.ldc;
     k.c_bstride = p.c_bstride;

@@ -1,0 +1,144 @@
+"""Host-side mirror of the reference's operator interface for the matmul path.
+
+Names, argument meaning and error behaviour follow src/native/src/ops/matmul.rs
+and the bias branch of src/native/src/ops/elementwise.rs; every function is a thin
+call into the C ABI of ``libmni_b200.so``.  Outputs are allocated here the way the
+reference's ``store.zeros`` does (uninitialised memory is fine: the kernels
+overwrite every element).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple
+
+from . import _lib
+from .tensor import DeviceTensor, current_stream, shape_size
+
+
+def broadcast_shape(a: Sequence[int], b: Sequence[int]) -> tuple:
+    """utils.rs:3-20.  Raises where the reference panics."""
+    nd = max(len(a), len(b))
+    out = []
+    for i in range(nd):
+        da = 1 if i < nd - len(a) else a[i - (nd - len(a))]
+        db = 1 if i < nd - len(b) else b[i - (nd - len(b))]
+        if da == db:
+            out.append(da)
+        elif da == 1:
+            out.append(db)
+        elif db == 1:
+            out.append(da)
+        else:
+            raise ValueError(f"shapes {list(a)} and {list(b)} are not broadcastable")
+    return tuple(out)
+
+
+def _matmul_out_shape(a: DeviceTensor, b: DeviceTensor) -> tuple:
+    if a.ndim < 2 or b.ndim < 2:
+        raise ValueError("matmul requires at least 2D tensors")          # ops/matmul.rs:89
+    if a.shape[-1] != b.shape[-2]:
+        raise ValueError(f"matmul inner dimensions must match: {a.shape[-1]} vs {b.shape[-2]}")  # :94
+    return broadcast_shape(a.shape[:-2], b.shape[:-2]) + (a.shape[-2], b.shape[-1])
+
+
+def matmul(a: DeviceTensor, b: DeviceTensor, bias: Optional[DeviceTensor] = None, *, flags: int = 0,
+           out: Optional[DeviceTensor] = None) -> DeviceTensor:
+    """``ops::matmul::matmul`` (ops/matmul.rs:83-197).  ``bias`` fuses the Linear bias add."""
+    oshape = _matmul_out_shape(a, b)
+    if bias is not None and (bias.ndim != 1 or bias.shape[0] != oshape[-1] or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous [N] vector")
+    if out is None:
+        out = DeviceTensor.empty(oshape, a.storage.device)
+    elif out.shape != oshape or not out.is_contiguous():
+        raise ValueError("out must be contiguous with the broadcast output shape")
+    va, vb = a.view_struct(), b.view_struct()
+    _lib.check(_lib.lib().mni_b200_matmul_fwd(va, vb, out.ptr, bias.ptr if bias is not None else None,
+                                              flags, current_stream()))
+    return out
+
+
+def matmul_backward(grad: DeviceTensor, a: DeviceTensor, b: DeviceTensor, *, flags: int = 0,
+                    need_da: bool = True, need_db: bool = True, want_dbias: bool = False,
+                    da: Optional[DeviceTensor] = None, db: Optional[DeviceTensor] = None,
+                    dbias: Optional[DeviceTensor] = None):
+    """``ops::matmul::matmul_backward`` (ops/matmul.rs:225-255) -> (grad_a, grad_b[, dbias])."""
+    oshape = _matmul_out_shape(a, b)
+    if grad.shape != oshape:
+        raise ValueError(f"grad has shape {grad.shape}, forward output is {oshape}")
+    dev = a.storage.device
+    if need_da and da is None:
+        da = DeviceTensor.empty(a.shape, dev)
+    if need_db and db is None:
+        db = DeviceTensor.empty(b.shape, dev)
+    if want_dbias and dbias is None:
+        dbias = DeviceTensor.empty((oshape[-1],), dev)
+    va, vb, vg = a.view_struct(), b.view_struct(), grad.view_struct()
+    _lib.check(_lib.lib().mni_b200_matmul_bwd(
+        va, vb, vg, da.ptr if need_da else None, db.ptr if need_db else None,
+        dbias.ptr if want_dbias else None, flags, current_stream()))
+    if want_dbias:
+        return da, db, dbias
+    return da, db
+
+
+def add(a: DeviceTensor, b: DeviceTensor) -> DeviceTensor:
+    """Bias branch of ``ops::elementwise::add`` (ops/elementwise.rs:105-130): [.., N] + [N]."""
+    if not (b.ndim == 1 and a.ndim >= 1 and a.shape[-1] == b.shape[0]):
+        raise NotImplementedError("only the Linear bias add ([..., N] + [N]) is on this path")
+    a = a.contiguous()
+    b = b.contiguous()
+    out = DeviceTensor.empty(a.shape, a.storage.device)
+    n = a.shape[-1]
+    rows = shape_size(a.shape[:-1])
+    _lib.check(_lib.lib().mni_b200_add_bias(a.ptr, b.ptr, out.ptr, rows, n, current_stream()))
+    return out
+
+
+def add_backward(grad: DeviceTensor, a_shape: Sequence[int], b_shape: Sequence[int], *,
+                 flags: int = 0) -> Tuple[DeviceTensor, DeviceTensor]:
+    """``add_backward`` for the bias branch (ops/elementwise.rs:213-231) -> (grad_a, grad_bias)."""
+    if tuple(grad.shape) != tuple(a_shape) or len(b_shape) != 1 or b_shape[0] != grad.shape[-1]:
+        raise NotImplementedError("only the Linear bias add ([..., N] + [N]) is on this path")
+    g = grad.contiguous()
+    ga = DeviceTensor.empty(a_shape, g.storage.device)
+    gb = DeviceTensor.empty(b_shape, g.storage.device)
+    n = g.shape[-1]
+    rows = shape_size(g.shape[:-1])
+    _lib.check(_lib.lib().mni_b200_add_bias_bwd(g.ptr, ga.ptr, gb.ptr, rows, n, flags, current_stream()))
+    return ga, gb
+
+
+class Linear:
+    """``Linear`` of src/nn.ts:8-26 over device tensors: y = x.W + b with W [in, out].
+
+    ``forward`` runs the drop-in sequence (matmul, then the stand-alone bias add, the
+    two N-API calls of nn.ts:24); ``forward_fused`` folds the bias into the GEMM epilogue.
+    """
+
+    def __init__(self, weight: DeviceTensor, bias: DeviceTensor):
+        if weight.ndim != 2 or bias.shape != (weight.shape[1],):
+            raise ValueError("weight must be [in, out] and bias [out]")
+        self.weight = weight
+        self.bias = bias
+
+    def forward(self, x: DeviceTensor) -> DeviceTensor:
+        return add(matmul(x, self.weight), self.bias)
+
+    def forward_fused(self, x: DeviceTensor, flags: int = 0) -> DeviceTensor:
+        return matmul(x, self.weight, self.bias, flags=flags)
+
+    def backward(self, x: DeviceTensor, dy: DeviceTensor, flags: int = 0):
+        """-> (dx, dW, db): add_backward then matmul_backward, with dbias fused into one call."""
+        dx, dw, dbias = matmul_backward(dy, x, self.weight, flags=flags, want_dbias=True)
+        return dx, dw, dbias
+
+
+def device_status() -> int:
+    """Synchronises the current stream; raises if a kernel recorded a bounded-wait timeout."""
+    import ctypes as C
+    detail = C.c_uint32(0)
+    _lib.check(_lib.lib().mni_b200_device_status(current_stream(), C.byref(detail)))
+    return int(detail.value)
+
+
+def launch_count() -> int:
+    return int(_lib.lib().mni_b200_launch_count())

@@ -1,0 +1,308 @@
+"""GPU parity tests: the CUDA library, called through its C ABI, against the CPU oracle on the
+same seeded inputs.  Default mode (3xTF32) must satisfy max|d| <= 1e-5 * K * max|a| * max|b|;
+the fast TF32 mode is held to a relative Frobenius error of 2e-3."""
+import numpy as np
+import pytest
+
+from conftest import rel_fro, tol_3xtf32
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def F():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    import framework_b200 as F
+    F._lib.lib()   # raises if the CUDA library is missing: there is no fallback
+    return F
+
+
+def _dev(F, arr):
+    return F.DeviceTensor.from_numpy(arr)
+
+
+def _check_fwd(F, O, a, b, *, perm_a=None, perm_b=None, bias=None, flags=0, fast=False):
+    """a, b: numpy arrays in storage layout; perm_*: stride-only permutation applied on both sides."""
+    ha, hb = O.HostTensor.from_array(a), O.HostTensor.from_array(b)
+    da, db = _dev(F, a), _dev(F, b)
+    if perm_a is not None:
+        ha, da = O.permute(ha, perm_a), da.permute(perm_a)
+    if perm_b is not None:
+        hb, db = O.permute(hb, perm_b), db.permute(perm_b)
+    ref = O.matmul(ha, hb)
+    if bias is not None:
+        ref = O.add(ref, O.HostTensor.from_array(bias))
+    out = F.matmul(da, db, _dev(F, bias) if bias is not None else None, flags=flags)
+    F.device_status()
+    got = out.numpy()
+    assert got.shape == tuple(ref.shape)
+    refn = ref.numpy()
+    k = ha.shape[-1]
+    if fast:
+        assert rel_fro(got, refn) <= 2e-3
+    else:
+        bound = tol_3xtf32(k, a, b) + (1e-6 * np.max(np.abs(bias)) if bias is not None else 0)
+        err = float(np.max(np.abs(got - refn))) if got.size else 0.0
+        assert err <= bound, f"max err {err:.3e} > bound {bound:.3e} for {a.shape} x {b.shape}"
+    return got
+
+
+def _check_bwd(F, O, a, b, g, *, perm_a=None, perm_b=None, flags=0, dbias=False):
+    ha, hb, hg = O.HostTensor.from_array(a), O.HostTensor.from_array(b), O.HostTensor.from_array(g)
+    da, db, dg = _dev(F, a), _dev(F, b), _dev(F, g)
+    if perm_a is not None:
+        ha, da = O.permute(ha, perm_a), da.permute(perm_a)
+    if perm_b is not None:
+        hb, db = O.permute(hb, perm_b), db.permute(perm_b)
+    ra, rb = O.matmul_backward(hg, ha, hb)
+    res = F.matmul_backward(dg, da, db, flags=flags, want_dbias=dbias)
+    F.device_status()
+    ga, gb = res[0].numpy(), res[1].numpy()
+    m, k, n = ha.shape[-2], ha.shape[-1], hb.shape[-1]
+    batch_a = int(np.prod(ha.shape[:-2])) if len(ha.shape) > 2 else 1
+    batch_b = int(np.prod(hb.shape[:-2])) if len(hb.shape) > 2 else 1
+    batch_g = int(np.prod(hg.shape[:-2])) if len(hg.shape) > 2 else 1
+    ka = n * max(1, batch_g // max(batch_a, 1))
+    kb = m * max(1, batch_g // max(batch_b, 1))
+    ea = float(np.max(np.abs(ga - ra.numpy())))
+    eb = float(np.max(np.abs(gb - rb.numpy())))
+    assert ea <= tol_3xtf32(ka, g, b), f"dA err {ea:.3e}"
+    assert eb <= tol_3xtf32(kb, a, g), f"dB err {eb:.3e}"
+    if dbias:
+        _, rbias = O.add_backward(hg, hg.shape, (n,))
+        ebias = float(np.max(np.abs(res[2].numpy() - rbias.numpy())))
+        assert ebias <= 1e-5 * (g.size // n) * float(np.max(np.abs(g)))
+    return ga, gb
+
+
+# ---------------------------------------------------------------------------------------------
+def test_reference_known_answers(F, oracle, golden):
+    for case in golden["forward"]:
+        a = np.array(case["a"]["data"], np.float32).reshape(case["a"]["shape"])
+        b = np.array(case["b"]["data"], np.float32).reshape(case["b"]["shape"])
+        for flags in (0, F._lib.FORCE_TENSOR_PATH):
+            got = F.matmul(_dev(F, a), _dev(F, b), flags=flags).numpy()
+            if "data" in case["out"]:
+                np.testing.assert_allclose(got.ravel(), case["out"]["data"], atol=case["tol"])
+            else:
+                assert abs(got.ravel()[0] - case["out"]["first"]) <= case["tol"]
+    for case in golden["backward"]:
+        a = np.array(case["a"]["data"], np.float32).reshape(case["a"]["shape"])
+        b = np.array(case["b"]["data"], np.float32).reshape(case["b"]["shape"])
+        g = np.array(case["grad"]["data"], np.float32).reshape(case["grad"]["shape"])
+        for flags in (0, F._lib.FORCE_TENSOR_PATH):
+            da, db = F.matmul_backward(_dev(F, g), _dev(F, a), _dev(F, b), flags=flags)
+            np.testing.assert_allclose(da.numpy().ravel(), case["da"], atol=1e-3)
+            np.testing.assert_allclose(db.numpy().ravel(), case["db"], atol=1e-3)
+
+
+def test_reference_shapes(F, golden):
+    rng = np.random.default_rng(0)
+    for case in golden["forward_shapes"]:
+        a = _dev(F, rng.random(case["a"], dtype=np.float32))
+        b = _dev(F, rng.random(case["b"], dtype=np.float32))
+        out = F.matmul(a, b)
+        if "bias" in case:
+            out = F.add(out, _dev(F, rng.random(case["bias"], dtype=np.float32)))
+        assert list(out.shape) == case["out"]
+
+
+def test_config1_square_512(F, oracle):
+    """A[512,512].B[512,512] ~N(0,1), seed 0, backward with dC = ones."""
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal((512, 512), dtype=np.float32)
+    b = rng.standard_normal((512, 512), dtype=np.float32)
+    _check_fwd(F, oracle, a, b)
+    _check_bwd(F, oracle, a, b, np.ones((512, 512), np.float32))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (2, 3, 7), (17, 33, 9), (31, 64, 65), (128, 128, 32),
+                                   (129, 130, 36), (127, 255, 100), (200, 300, 64), (256, 257, 132),
+                                   (64, 520, 40), (300, 72, 260)])
+def test_odd_shapes_fwd_bwd(F, oracle, m, n, k):
+    rng = np.random.default_rng(m * 10007 + n * 101 + k)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    g = rng.standard_normal((m, n), dtype=np.float32)
+    flags = F._lib.FORCE_TENSOR_PATH
+    _check_fwd(F, oracle, a, b, flags=flags)
+    _check_bwd(F, oracle, a, b, g, flags=flags, dbias=True)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+def test_all_four_major_combinations(F, oracle, ta, tb):
+    """Transposed operands are stride-only views: the kernel reads them through its descriptors."""
+    rng = np.random.default_rng(11)
+    m, k, n = 192, 160, 320
+    a = rng.standard_normal((k, m) if ta else (m, k), dtype=np.float32)
+    b = rng.standard_normal((n, k) if tb else (k, n), dtype=np.float32)
+    _check_fwd(F, oracle, a, b, perm_a=[1, 0] if ta else None, perm_b=[1, 0] if tb else None,
+               flags=F._lib.FORCE_TENSOR_PATH)
+    g = rng.standard_normal((m, n), dtype=np.float32)
+    _check_bwd(F, oracle, a, b, g, perm_a=[1, 0] if ta else None, perm_b=[1, 0] if tb else None,
+               flags=F._lib.FORCE_TENSOR_PATH)
+
+
+def test_batched_and_broadcast(F, oracle):
+    rng = np.random.default_rng(12)
+    a = rng.standard_normal((4, 3, 40, 24), dtype=np.float32)
+    b = rng.standard_normal((4, 3, 24, 56), dtype=np.float32)
+    _check_fwd(F, oracle, a, b)
+    _check_bwd(F, oracle, a, b, rng.standard_normal((4, 3, 40, 56), dtype=np.float32))
+    w = rng.standard_normal((24, 56), dtype=np.float32)          # shared weight
+    _check_fwd(F, oracle, a, w)
+    _check_bwd(F, oracle, a, w, rng.standard_normal((4, 3, 40, 56), dtype=np.float32))
+    x = rng.standard_normal((40, 24), dtype=np.float32)          # shared left operand
+    _check_fwd(F, oracle, x, b)
+    _check_bwd(F, oracle, x, b, rng.standard_normal((4, 3, 40, 56), dtype=np.float32))
+
+
+def test_non_simple_broadcast_matches_reference_indexing(F, oracle):
+    rng = np.random.default_rng(13)
+    a = rng.standard_normal((2, 1, 20, 12), dtype=np.float32)
+    b = rng.standard_normal((1, 3, 12, 28), dtype=np.float32)
+    _check_fwd(F, oracle, a, b)
+    _check_bwd(F, oracle, a, b, rng.standard_normal((2, 3, 20, 28), dtype=np.float32))
+
+
+def test_attention_shaped_strided_k(F, oracle):
+    """Config 3 at reduced size: S = Q.K^T with K^T a permute(0,1,3,2) view, then S.V, and backward."""
+    rng = np.random.default_rng(14)
+    bsz, h, s, d = 2, 3, 128, 64
+    q = rng.standard_normal((bsz, h, s, d), dtype=np.float32)
+    k = rng.standard_normal((bsz, h, s, d), dtype=np.float32)
+    v = rng.standard_normal((bsz, h, s, d), dtype=np.float32)
+    sc = _check_fwd(F, oracle, q, k, perm_b=[0, 1, 3, 2])
+    _check_fwd(F, oracle, sc, v)
+    d_o = rng.standard_normal((bsz, h, s, d), dtype=np.float32)
+    d_s, _ = _check_bwd(F, oracle, sc, v, d_o)
+    _check_bwd(F, oracle, q, k, d_s, perm_b=[0, 1, 3, 2])
+
+
+def test_head_split_view_with_two_batch_strides(F, oracle):
+    """[B,S,H,D] -> permute(0,2,1,3): batch dims that do not collapse into one stride."""
+    rng = np.random.default_rng(15)
+    x = rng.standard_normal((2, 48, 3, 32), dtype=np.float32)
+    w = rng.standard_normal((2, 3, 32, 40), dtype=np.float32)
+    _check_fwd(F, oracle, x, w, perm_a=[0, 2, 1, 3])
+    _check_bwd(F, oracle, x, w, rng.standard_normal((2, 3, 48, 40), dtype=np.float32), perm_a=[0, 2, 1, 3])
+
+
+def test_linear_layer_fused_and_drop_in(F, oracle):
+    """Config 2 at reduced size: y = x.W + b, backward gives dx, dW, db."""
+    rng = np.random.default_rng(16)
+    x = rng.random((384, 256), dtype=np.float32)
+    w = (0.02 * rng.standard_normal((256, 512))).astype(np.float32)
+    dy = rng.standard_normal((384, 512), dtype=np.float32)
+    for bias in (np.zeros(512, np.float32), (0.02 * rng.standard_normal(512)).astype(np.float32)):
+        fused = _check_fwd(F, oracle, x, w, bias=bias)
+        lin = F.Linear(_dev(F, w), _dev(F, bias))
+        two_step = lin.forward(_dev(F, x)).numpy()
+        assert float(np.max(np.abs(two_step - fused))) <= 1e-6
+    _check_bwd(F, oracle, x, w, dy, dbias=True)
+    ga, gb = F.add_backward(_dev(F, dy), dy.shape, (512,))
+    ra, rb = oracle.add_backward(oracle.HostTensor.from_array(dy), dy.shape, (512,))
+    assert np.array_equal(ga.numpy(), ra.numpy())
+    assert float(np.max(np.abs(gb.numpy() - rb.numpy()))) <= 1e-5 * 384 * float(np.max(np.abs(dy)))
+
+
+def test_broadcast_weight_gradient_is_reduced_in_the_gemm(F, oracle):
+    """Config 4 at reduced size: dW sums over the batch broadcast."""
+    rng = np.random.default_rng(17)
+    a = rng.standard_normal((6, 100, 96), dtype=np.float32)
+    w = (0.02 * rng.standard_normal((96, 200))).astype(np.float32)
+    _check_fwd(F, oracle, a, w)
+    _check_bwd(F, oracle, a, w, rng.standard_normal((6, 100, 200), dtype=np.float32))
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_skinny_rows(F, oracle, m):
+    """Config 5b at reduced size, on the skinny path and forced onto the tensor path."""
+    rng = np.random.default_rng(18 + m)
+    x = rng.standard_normal((m, 512), dtype=np.float32)
+    w = rng.standard_normal((512, 768), dtype=np.float32)
+    dy = rng.standard_normal((m, 768), dtype=np.float32)
+    for flags in (0, F._lib.FORCE_TENSOR_PATH):
+        _check_fwd(F, oracle, x, w, flags=flags)
+        _check_bwd(F, oracle, x, w, dy, flags=flags)
+    bias = rng.standard_normal(768, dtype=np.float32)
+    _check_fwd(F, oracle, x, w, bias=bias)
+
+
+def test_forced_split_k_and_pack_paths(F, oracle):
+    rng = np.random.default_rng(19)
+    a = rng.standard_normal((150, 700), dtype=np.float32)
+    b = rng.standard_normal((700, 90), dtype=np.float32)
+    for flags in (F._lib.force_split_k(3), F._lib.force_split_k(7), F._lib.FORCE_PACK,
+                  F._lib.FORCE_PACK | F._lib.force_split_k(2)):
+        _check_fwd(F, oracle, a, b, flags=flags | F._lib.FORCE_TENSOR_PATH)
+    _check_fwd(F, oracle, a, b, bias=rng.standard_normal(90, dtype=np.float32),
+               flags=F._lib.force_split_k(4) | F._lib.FORCE_TENSOR_PATH)
+
+
+def test_accumulate_flags(F, oracle):
+    rng = np.random.default_rng(20)
+    a = rng.standard_normal((70, 50), dtype=np.float32)
+    b = rng.standard_normal((50, 60), dtype=np.float32)
+    g = rng.standard_normal((70, 60), dtype=np.float32)
+    base_c = rng.standard_normal((70, 60), dtype=np.float32)
+    out = _dev(F, base_c)
+    F.matmul(_dev(F, a), _dev(F, b), flags=F._lib.ACCUMULATE_C | F._lib.FORCE_TENSOR_PATH, out=out)
+    ref = base_c + oracle.matmul(oracle.HostTensor.from_array(a), oracle.HostTensor.from_array(b)).numpy()
+    assert float(np.max(np.abs(out.numpy() - ref))) <= tol_3xtf32(50, a, b)
+    base_a, base_b = rng.standard_normal(a.shape, dtype=np.float32), rng.standard_normal(b.shape, dtype=np.float32)
+    da, db = _dev(F, base_a), _dev(F, base_b)
+    F.matmul_backward(_dev(F, g), _dev(F, a), _dev(F, b), da=da, db=db,
+                      flags=F._lib.ACCUMULATE_DA | F._lib.ACCUMULATE_DB | F._lib.FORCE_TENSOR_PATH)
+    ra, rb = oracle.matmul_backward(oracle.HostTensor.from_array(g), oracle.HostTensor.from_array(a),
+                                    oracle.HostTensor.from_array(b))
+    assert float(np.max(np.abs(da.numpy() - (base_a + ra.numpy())))) <= tol_3xtf32(60, g, b)
+    assert float(np.max(np.abs(db.numpy() - (base_b + rb.numpy())))) <= tol_3xtf32(70, a, g)
+
+
+def test_fast_tf32_mode(F, oracle):
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((256, 384), dtype=np.float32)
+    b = rng.standard_normal((384, 320), dtype=np.float32)
+    _check_fwd(F, oracle, a, b, flags=F._lib.PRECISION_TF32 | F._lib.FORCE_TENSOR_PATH, fast=True)
+
+
+def test_outputs_are_fully_overwritten(F, oracle):
+    """store.zeros may hand back a dirty buffer (allocator.rs:61-66): stale contents must not leak."""
+    import torch
+    rng = np.random.default_rng(22)
+    a = rng.standard_normal((100, 36), dtype=np.float32)
+    b = rng.standard_normal((36, 44), dtype=np.float32)
+    out = F.DeviceTensor(torch.full((100 * 44,), float("nan"), device="cuda"), (100, 44))
+    F.matmul(_dev(F, a), _dev(F, b), out=out, flags=F._lib.FORCE_TENSOR_PATH)
+    assert np.isfinite(out.numpy()).all()
+
+
+def test_empty_and_degenerate(F, oracle):
+    a0 = F.DeviceTensor.empty((0, 8))
+    b = _dev(F, np.ones((8, 4), np.float32))
+    assert F.matmul(a0, b).shape == (0, 4)
+    az = F.DeviceTensor.empty((5, 0))
+    bz = F.DeviceTensor.empty((0, 4))
+    out = F.matmul(az, bz)
+    assert out.shape == (5, 4) and not out.numpy().any()
+
+
+def test_linearity_at_full_size_config2(F):
+    """Size-independent property at the bench workload's full size: (a1 + a2).W == a1.W + a2.W."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x1 = torch.rand((4096, 1024), device="cuda", generator=g)
+    x2 = torch.rand((4096, 1024), device="cuda", generator=g)
+    w = 0.02 * torch.randn((1024, 4096), device="cuda", generator=g)
+    t = F.DeviceTensor.from_torch
+    y12 = F.matmul(t(x1 + x2), t(w)).torch_view()
+    y1 = F.matmul(t(x1), t(w)).torch_view()
+    y2 = F.matmul(t(x2), t(w)).torch_view()
+    F.device_status()
+    bound = 1e-5 * 1024 * 2.0 * float(w.abs().max())
+    assert float((y12 - y1 - y2).abs().max()) <= 3 * bound
+    ref = (x1.double() @ w.double())
+    assert float((y1.double() - ref).abs().max()) <= 1e-5 * 1024 * 1.0 * float(w.abs().max())

@@ -1,0 +1,154 @@
+"""CPU: the oracle against the reference's own known answers and against independent maths."""
+import numpy as np
+import pytest
+
+
+def _t(O, shape, data):
+    return O.HostTensor.from_array(np.array(data, np.float32).reshape(shape))
+
+
+def test_reference_forward_known_answers(oracle, golden):
+    O = oracle
+    for case in golden["forward"]:
+        out = O.matmul(_t(O, **case["a"]), _t(O, **case["b"]), threads=1)
+        assert list(out.shape) == case["out"]["shape"], case["source"]
+        if "data" in case["out"]:
+            np.testing.assert_allclose(out.data, case["out"]["data"], atol=case["tol"])
+        else:
+            assert abs(out.data[0] - case["out"]["first"]) <= case["tol"]
+
+
+def test_reference_forward_shapes(oracle, golden):
+    O = oracle
+    rng = np.random.default_rng(1)
+    for case in golden["forward_shapes"]:
+        a = O.HostTensor.from_array(rng.random(case["a"], dtype=np.float32))
+        b = O.HostTensor.from_array(rng.random(case["b"], dtype=np.float32))
+        out = O.matmul(a, b)
+        if "bias" in case:
+            out = O.add(out, O.HostTensor.from_array(rng.random(case["bias"], dtype=np.float32)))
+        assert list(out.shape) == case["out"], case["source"]
+
+
+def test_reference_backward_known_answers(oracle, golden):
+    O = oracle
+    for case in golden["backward"]:
+        da, db = O.matmul_backward(_t(O, **case["grad"]), _t(O, **case["a"]), _t(O, **case["b"]), threads=1)
+        np.testing.assert_array_equal(da.data, np.array(case["da"], np.float32))
+        np.testing.assert_array_equal(db.data, np.array(case["db"], np.float32))
+
+
+@pytest.mark.parametrize("shape_a,shape_b", [((64, 48), (48, 40)), ((3, 17, 9), (3, 9, 11)),
+                                             ((5, 8, 16), (16, 12)), ((7, 6), (2, 6, 5))])
+def test_threads_are_bit_identical(oracle, shape_a, shape_b):
+    O = oracle
+    rng = np.random.default_rng(2)
+    a = O.HostTensor.from_array(rng.standard_normal(shape_a, dtype=np.float32))
+    b = O.HostTensor.from_array(rng.standard_normal(shape_b, dtype=np.float32))
+    c1 = O.matmul(a, b, threads=1)
+    c4 = O.matmul(a, b, threads=4)
+    assert np.array_equal(c1.data, c4.data)
+    g = O.HostTensor.from_array(rng.standard_normal(c1.shape, dtype=np.float32))
+    da1, db1 = O.matmul_backward(g, a, b, threads=1)
+    da4, db4 = O.matmul_backward(g, a, b, threads=4)
+    assert np.array_equal(da1.data, da4.data) and np.array_equal(db1.data, db4.data)
+
+
+def test_loop_order_is_k_ascending_without_fma(oracle):
+    """One output element must equal the sequential f32 mul-then-add chain of ops/matmul.rs:62-68."""
+    O = oracle
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((4, 300), dtype=np.float32)
+    b = rng.standard_normal((300, 5), dtype=np.float32)
+    out = O.matmul(O.HostTensor.from_array(a), O.HostTensor.from_array(b), threads=1).data.reshape(4, 5)
+    for i, j in [(0, 0), (3, 4), (2, 1)]:
+        acc = np.float32(0.0)
+        for k in range(300):
+            acc = np.float32(acc + np.float32(a[i, k] * b[k, j]))
+        assert out[i, j] == acc
+
+
+def test_matches_float64_closely(oracle):
+    O = oracle
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal((6, 33, 70), dtype=np.float32)
+    b = rng.standard_normal((70, 21), dtype=np.float32)
+    out = O.matmul(O.HostTensor.from_array(a), O.HostTensor.from_array(b)).numpy()
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    assert np.max(np.abs(out - ref)) < 1e-4
+    g = rng.standard_normal(out.shape, dtype=np.float32)
+    da, db = O.matmul_backward(O.HostTensor.from_array(g), O.HostTensor.from_array(a), O.HostTensor.from_array(b))
+    np.testing.assert_allclose(da.numpy(), g.astype(np.float64) @ b.T.astype(np.float64), atol=2e-4)
+    dbr = np.einsum("bmk,bmn->kn", a.astype(np.float64), g.astype(np.float64))
+    np.testing.assert_allclose(db.numpy(), dbr, atol=1e-3)
+
+
+def test_strided_views_are_gathered(oracle):
+    """permute gives a stride-only view (ops/layout.rs:112-134); matmul reads it through ensure_contiguous."""
+    O = oracle
+    rng = np.random.default_rng(5)
+    q = rng.standard_normal((2, 3, 8, 4), dtype=np.float32)
+    k = rng.standard_normal((2, 3, 8, 4), dtype=np.float32)
+    kt = O.permute(O.HostTensor.from_array(k), [0, 1, 3, 2])
+    assert kt.shape == (2, 3, 4, 8) and kt.strides == (96, 32, 1, 4) and not kt.is_contiguous()
+    s = O.matmul(O.HostTensor.from_array(q), kt).numpy()
+    np.testing.assert_allclose(s, q @ np.swapaxes(k, -1, -2), atol=1e-5)
+    g = O.HostTensor.from_array(np.ones((2, 3, 4, 8), np.float32))
+    back = O.permute_backward(g, [0, 1, 3, 2], (2, 3, 8, 4))
+    assert back.shape == (2, 3, 8, 4)
+
+
+def test_non_simple_broadcast_uses_modulo_indexing(oracle):
+    """ops/matmul.rs:55-56: operand batch index is `batch % operand_batch`, not true N-D broadcasting."""
+    O = oracle
+    rng = np.random.default_rng(6)
+    a = rng.standard_normal((2, 1, 3, 4), dtype=np.float32)
+    b = rng.standard_normal((1, 3, 4, 5), dtype=np.float32)
+    out = O.matmul(O.HostTensor.from_array(a), O.HostTensor.from_array(b)).numpy()
+    assert out.shape == (2, 3, 3, 5)
+    flat = out.reshape(6, 3, 5)
+    for batch in range(6):
+        np.testing.assert_allclose(flat[batch], a.reshape(2, 3, 4)[batch % 2] @ b.reshape(3, 4, 5)[batch % 3],
+                                   atol=1e-5)
+
+
+def test_unbroadcast_backward_of_shared_weight(oracle):
+    O = oracle
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((5, 6, 7), dtype=np.float32)
+    w = rng.standard_normal((7, 3), dtype=np.float32)
+    g = rng.standard_normal((5, 6, 3), dtype=np.float32)
+    da, dw = O.matmul_backward(O.HostTensor.from_array(g), O.HostTensor.from_array(a), O.HostTensor.from_array(w),
+                               threads=1)
+    assert da.shape == (5, 6, 7) and dw.shape == (7, 3)
+    # two-level order of the reference: per-batch products, then batches added in ascending order
+    per = np.stack([a[i].T.astype(np.float64) @ g[i].astype(np.float64) for i in range(5)])
+    np.testing.assert_allclose(dw.numpy(), per.sum(0), atol=1e-4)
+
+
+def test_bias_add_and_backward(oracle):
+    O = oracle
+    rng = np.random.default_rng(8)
+    y = rng.standard_normal((4, 6), dtype=np.float32)
+    bias = rng.standard_normal((6,), dtype=np.float32)
+    out = O.add(O.HostTensor.from_array(y), O.HostTensor.from_array(bias))
+    assert np.array_equal(out.numpy(), y + bias)
+    g = rng.standard_normal((4, 6), dtype=np.float32)
+    ga, gb = O.add_backward(O.HostTensor.from_array(g), (4, 6), (6,), threads=1)
+    assert np.array_equal(ga.numpy(), g)
+    acc = np.zeros(6, np.float32)
+    for r in range(4):
+        acc = (acc + g[r]).astype(np.float32)
+    assert np.array_equal(gb.numpy(), acc)
+
+
+def test_error_cases(oracle):
+    O = oracle
+    a = O.HostTensor.from_array(np.zeros((2, 3), np.float32))
+    with pytest.raises(ValueError, match="inner dimensions"):
+        O.matmul(a, O.HostTensor.from_array(np.zeros((4, 2), np.float32)))
+    with pytest.raises(ValueError, match="at least 2D"):
+        O.matmul(a, O.HostTensor.from_array(np.zeros((3,), np.float32)))
+    with pytest.raises(ValueError, match="broadcastable"):
+        O.matmul(O.HostTensor.from_array(np.zeros((2, 2, 3), np.float32)),
+                 O.HostTensor.from_array(np.zeros((3, 3, 2), np.float32)))
