@@ -7,10 +7,11 @@
 //               128B/64B-swizzled shared-memory stage.  K-major and MN-major operands
 //               differ only in the tensor map and the box list, so transposed / permuted
 //               operands are read in place -- no transposed copy is ever written.
-//   warps 2-5   split: every f32 of the landed stage is split into hi (low 13 mantissa
-//               bits cleared, a valid TF32) and lo = x - hi (exact), hi in place, lo into
-//               a sibling buffer of identical layout (the split is position independent,
-//               so it needs no knowledge of the swizzle).
+//   warps 2-5   split: for every f32 x of the landed stage, lo = x - trunc_tf32(x) (exact in
+//               f32) is written to a sibling buffer of identical layout (the split is position
+//               independent, so it needs no knowledge of the swizzle).  The landed tile itself
+//               serves as hi: the tensor core ignores the low 13 mantissa bits of a TF32
+//               operand (tests/test_matmul_gpu.py pins that behaviour).
 //   warp 1      one thread issues tcgen05.mma.kind::tf32 per 8-deep k-step:
 //               lo*hi, hi*lo, hi*hi into one f32 accumulator in TMEM ("3xTF32").  In the
 //               optional fast mode the split warps idle and one MMA per k-step is issued
@@ -350,17 +351,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     float4 *lo = raw + n4;
 #pragma unroll 4
                     for (int i = tid; i < n4; i += 128) {
+                        // The tensor core reads only the TF32 bits of a 32-bit operand (the low 13
+                        // mantissa bits are ignored), so the landed tile already is "hi"; only the
+                        // residual lo = x - trunc(x), exact in f32, has to be written.
                         const float4 v = raw[i];
-                        float4 h, l;
-                        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
-                        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-                        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
-                        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-                        l.x = v.x - h.x;
-                        l.y = v.y - h.y;
-                        l.z = v.z - h.z;
-                        l.w = v.w - h.w;
-                        raw[i] = h;
+                        float4 l;
+                        l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+                        l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+                        l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+                        l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
                         lo[i] = l;
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

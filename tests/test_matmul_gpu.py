@@ -269,6 +269,31 @@ def test_fast_tf32_mode(F, oracle):
     _check_fwd(F, oracle, a, b, flags=F._lib.PRECISION_TF32 | F._lib.FORCE_TENSOR_PATH, fast=True)
 
 
+def test_tensor_core_ignores_low_mantissa_bits(F):
+    """The 3xTF32 split uses the raw f32 tile as its "hi" part, which is only right if the tensor core
+    truncates (ignores the low 13 mantissa bits of) a TF32 operand.  Pin that: single-pass TF32 on raw
+    inputs must be bit-identical to single-pass TF32 on inputs whose low 13 bits were cleared."""
+    rng = np.random.default_rng(23)
+    a = rng.standard_normal((256, 192), dtype=np.float32)
+    b = rng.standard_normal((192, 320), dtype=np.float32)
+    mask = np.uint32(0xFFFFE000)
+    am = (a.view(np.uint32) & mask).view(np.float32)
+    bm = (b.view(np.uint32) & mask).view(np.float32)
+    flags = F._lib.PRECISION_TF32 | F._lib.FORCE_TENSOR_PATH
+    raw = F.matmul(_dev(F, a), _dev(F, b), flags=flags).numpy()
+    cut = F.matmul(_dev(F, am), _dev(F, bm), flags=flags).numpy()
+    F.device_status()
+    assert np.array_equal(raw, cut)
+    for perm_a, perm_b in (([1, 0], None), (None, [1, 0])):     # MN-major A, K-major B
+        at, bt = np.ascontiguousarray(a.T), np.ascontiguousarray(b.T)
+        atm, btm = np.ascontiguousarray(am.T), np.ascontiguousarray(bm.T)
+        x = _dev(F, at).permute(perm_a) if perm_a else _dev(F, a)
+        y = _dev(F, bt).permute(perm_b) if perm_b else _dev(F, b)
+        xm = _dev(F, atm).permute(perm_a) if perm_a else _dev(F, am)
+        ym = _dev(F, btm).permute(perm_b) if perm_b else _dev(F, bm)
+        assert np.array_equal(F.matmul(x, y, flags=flags).numpy(), F.matmul(xm, ym, flags=flags).numpy())
+
+
 def test_outputs_are_fully_overwritten(F, oracle):
     """store.zeros may hand back a dirty buffer (allocator.rs:61-66): stale contents must not leak."""
     import torch
