@@ -55,6 +55,8 @@ _SIGNATURES = {
                                       C.c_void_p, C.c_uint32, C.c_void_p]),
     "mni_b200_add_bias": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "mni_b200_add_bias_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_uint32, C.c_void_p]),
+    "mni_b200_add_bias_bwd_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_uint32,
+                                                C.c_void_p]),
     "mni_b200_contiguous": (C.c_int, [C.POINTER(View), C.c_void_p, C.c_void_p]),
     "mni_b200_workspace_set": (C.c_int, [C.c_void_p, C.c_size_t]),
     "mni_b200_workspace_query": (C.c_int, [C.POINTER(View), C.POINTER(View), C.c_uint32, C.POINTER(C.c_size_t)]),

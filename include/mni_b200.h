@@ -130,6 +130,26 @@ MNI_B200_API int mni_b200_add_bias_bwd(const float *dy, float *d_y, float *dbias
                           uint32_t flags, void *stream);
 
 /*
+ * Same result as mni_b200_add_bias_bwd, for callers that must never see this library
+ * allocate device memory: a runtime that owns the device's memory budget through its own
+ * allocator, or a step loop that cannot take the device-wide stall of cudaMalloc/cudaFree.
+ * (No counterpart in the reference: it is an addition of this library.)
+ *
+ * The partial column sums live in a fixed 1 MiB array inside the library's device image
+ * instead of the growable scratch buffer, so this call performs no allocation of any kind.
+ *   - Sizes whose partial sums exceed 1 MiB are refused with MNI_B200_ERR_WORKSPACE before
+ *     anything is launched (every n <= 262144 fits).
+ *   - All calls on a device share that array and it keeps the previous call's contents;
+ *     no slot needs to start at zero, each call overwrites what it later reads.
+ *   - Calls that overlap on the GPU (other streams / unordered threads) race on the array:
+ *     keep them on one stream or order them with events.
+ *   - The first call on each device resolves and caches the array's device address; make
+ *     that call at start-up, before any stream capture begins on that device.
+ */
+MNI_B200_API int mni_b200_add_bias_bwd_noalloc(const float *dy, float *d_y, float *dbias, int64_t rows,
+                                               int64_t n, uint32_t flags, void *stream);
+
+/*
  * Device-side gather of a strided view into a contiguous row-major buffer.
  * Replaces TensorStore::ensure_contiguous on the CUDA backend
  * (tensor.rs:510-517, a device->host->device round trip in the reference).
