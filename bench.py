@@ -104,8 +104,8 @@ def shard_workload(wl: Workload, world: int) -> Workload:
     c5a.  c2 is weak-scaled (every rank owns a full-size batch shard), the rest run as replicas."""
     if world == 1 or wl.name not in ("c4", "c5a"):
         return wl
-    a_shape = list(wl.a_shape)
-    a_shape[0] //= world
+    from framework_b200.sharding import shard_leading
+    a_shape = shard_leading(wl.a_shape, int(os.environ.get("RANK", "0")), world)
     return Workload(wl.name, wl.desc + f" (1/{world} shard)", a_shape, wl.b_shape, bias=wl.bias,
                     b_perm=wl.b_perm, dist_a=wl.dist_a, dist_b=wl.dist_b, scale_b=wl.scale_b)
 
@@ -161,6 +161,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     import framework_b200 as F
+    from framework_b200.sharding import reduce_to_root
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -195,9 +196,9 @@ def run_ours(args):
         F.matmul(a, b, bias, flags=flags, out=y)
         F.matmul_backward(dy, a, b, flags=flags, da=da, db=db, dbias=dbias, want_dbias=wl.bias)
         if reduce_grads:
-            dist.reduce(db.storage, dst=0)
+            reduce_to_root(db.storage, dst=0)
             if dbias is not None:
-                dist.reduce(dbias.storage, dst=0)
+                reduce_to_root(dbias.storage, dst=0)
 
     def barrier():
         if world > 1:
