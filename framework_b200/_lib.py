@@ -63,6 +63,7 @@ _SIGNATURES = {
     "mni_b200_device_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "mni_b200_launch_count": (C.c_uint64, []),
     "mni_b200_release": (C.c_int, []),
+    "mni_b200_role_wait_cycles": (C.c_int, [C.POINTER(C.c_uint64), C.c_int]),
 }
 
 

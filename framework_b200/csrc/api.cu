@@ -637,6 +637,11 @@ int mni_b200_device_status(void *stream, uint32_t *detail) {
     return MNI_B200_OK;
 }
 
+int mni_b200_role_wait_cycles(uint64_t out[8], int reset) {
+    if (!out) return fail(MNI_B200_ERR_ARG, "out is null");
+    return read_role_waits(out, reset);
+}
+
 int mni_b200_release(void) {
     DeviceState *st = nullptr;
     int rc = device_state(&st);

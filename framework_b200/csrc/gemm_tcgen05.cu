@@ -2,11 +2,11 @@
 //
 // Data path of one CTA (persistent over output tiles, one CTA per SM):
 //
-//   warp 0      TMA producer: cp.async.bulk.tensor (5-D maps: 2 matrix dims + up to 3
-//               batch dims) brings a 128 x BK tile of A and a BN x BK tile of B into a
-//               128B/64B-swizzled shared-memory stage.  K-major and MN-major operands
-//               differ only in the tensor map and the box list, so transposed / permuted
-//               operands are read in place -- no transposed copy is ever written.
+//   warp 0      TMA producer: cp.async.bulk.tensor (5-D maps: matrix dims + batch dims) brings
+//               a 128 x BK tile of A and a BN x BK tile of B into a swizzled shared-memory
+//               stage.  K-major and MN-major operands differ only in the tensor map and the
+//               box list, so transposed / permuted operands are read in place -- no transposed
+//               copy is ever written.
 //   warps 2-5   split: for every f32 x of the landed stage, lo = x - trunc_tf32(x) (exact in
 //               f32) is written to a sibling buffer of identical layout (the split is position
 //               independent, so it needs no knowledge of the swizzle).  The landed tile itself
@@ -15,11 +15,15 @@
 //   warp 1      one thread issues tcgen05.mma.kind::tf32 per 8-deep k-step:
 //               lo*hi, hi*lo, hi*hi into one f32 accumulator in TMEM ("3xTF32").  In the
 //               optional fast mode the split warps idle and one MMA per k-step is issued
-//               on the raw tile.
-//   warps 6-9   epilogue: tcgen05.ld of the 128 x BN accumulator (double buffered in
-//               TMEM, so it overlaps the next tile's main loop), transposed through a
-//               padded smem patch so that global stores are row-contiguous 16-byte
-//               vectors; bias add / accumulate / split-K partial output are fused here.
+//               on the raw tile.  Issuing one MMA costs this thread ~120 cycles, about what
+//               a 128 x 256 x 8 MMA takes to execute, so the loop is fully unrolled and keeps
+//               its per-stage bookkeeping to a wait, a fence and a commit.
+//   warps 6-9   epilogue: tcgen05.ld of the 128 x BN accumulator (double buffered in TMEM, so it
+//               overlaps the next tile's main loop), bias add in registers, 128B-swizzled
+//               staging patch in shared memory, TMA store (or TMA reduce-add for C += ...) of
+//               32 x 32 boxes; the tensor map clips the M / N tails.  Split-K partials go
+//               through the same path into scratch.  Outputs whose row pitch is not a multiple
+//               of 16 bytes take a plain-store fallback.
 //
 // Every wait on an mbarrier is bounded: after ~2 s worth of clock cycles the waiter
 // records a code in a global error word, raises a CTA-wide abort flag and all roles
@@ -36,9 +40,13 @@ namespace {
 constexpr int BM = 128;
 constexpr int kThreads = 320;
 constexpr int kMaxStages = 8;
-constexpr int kEpiPitch = 36;                        // floats per staged row (32 + 4 pad)
-constexpr int kEpiBytes = 4 * 32 * kEpiPitch * 4;    // 4 epilogue warps
-constexpr long long kWaitCycles = 4000000000LL;      // ~2 s at 2 GHz
+constexpr int kEpiBufBytes = 32 * 128;                     // one 32 x 32 f32 patch
+constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;            // 4 epilogue warps, double buffered
+constexpr int kBarBytes = (3 * kMaxStages + 4) * 8 + 16;
+constexpr long long kWaitCycles = 4000000000LL;            // ~2 s at 2 GHz
+
+enum OperandMode { kKMajor = 0, kMnMultiBox = 1, kMnSingleBox = 2 };
+enum EpilogueMode { kEpiPlainStores = 0, kEpiTmaStore = 1, kEpiTmaReduce = 2 };
 
 struct KParams {
     int M, N;
@@ -49,23 +57,20 @@ struct KParams {
     int splits;
     int a_batch, a_d1, a_d2;   // operand flat batch count and inner dim sizes
     int b_batch, b_d1, b_d2;
-    int a_kmajor, b_kmajor;
-    int bn, bk;
+    int a_mode, b_mode;        // OperandMode
     int stages;
-    int fast;
+    int epi_mode;              // EpilogueMode
     uint32_t idesc;
-    uint32_t a_bytes, b_bytes; // raw bytes of one stage's A / B tile
-    uint32_t stage_bytes;      // whole stage incl. lo copies
-    // smem descriptor constants (without start address)
-    uint64_t a_desc_hi, b_desc_hi;   // upper 32 bits pre-shifted | version | layout
-    uint32_t a_desc_lbo, b_desc_lbo; // (lbo >> 4) << 16, lives in the low word
-    uint32_t a_kstep, b_kstep;       // descriptor address advance (16-byte units) per k-step
+    uint32_t a_desc_hi, b_desc_hi;   // upper 32 bits of the smem descriptors (SBO | version | layout)
+    uint32_t a_desc_lbo, b_desc_lbo; // LBO field, already shifted into the low word
+    uint32_t a_kstep, b_kstep;       // descriptor address advance (16-byte units) per 8-deep k-step
     float *C;
     long long ldc, c_bstride;
     float *partial;            // split-K: [split][batch][M][N]
     const float *bias;
     int accumulate;
     unsigned int *err;
+    unsigned long long *prof;  // optional role wait counters (null = off)
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -94,13 +99,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 // Bounded wait.  Returns false if the CTA is aborting (this waiter or another gave up).
+// `waited` accumulates the cycles spent blocked (role-level wait accounting).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          unsigned int *err, uint32_t code) {
-    if (mbar_try_wait(bar, parity)) return true;
+                                          unsigned int *err, uint32_t code, long long &waited) {
     const long long t0 = clock64();
+    if (mbar_try_wait(bar, parity)) {
+        waited += clock64() - t0;
+        return true;
+    }
     uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity)) {
+            waited += clock64() - t0;
+            return true;
+        }
         if ((++spins & 63u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > kWaitCycles) {
@@ -120,13 +132,26 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map
         "r"(c4)
         : "memory");
 }
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
+__device__ __forceinline__ void tma_store_5d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(0), "r"(0)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_5d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "cp.reduce.async.bulk.tensor.5d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(0), "r"(0)
+        : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                          uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -139,7 +164,7 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -151,6 +176,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
           "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
@@ -172,10 +199,24 @@ __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit) {
     const int rin = r - g * group_sz;
     t.tn = rin / gm;
     t.tm = first_m + (rin - t.tn * gm);
-    const long long total = static_cast<long long>(p.fold) * p.kiters;
-    t.it0 = static_cast<int>(total * t.split / p.splits);
-    t.it1 = static_cast<int>(total * (t.split + 1) / p.splits);
+    const int total = p.fold * p.kiters;
+    if (p.splits == 1) {
+        t.it0 = 0;
+        t.it1 = total;
+    } else {
+        t.it0 = static_cast<int>(static_cast<long long>(total) * t.split / p.splits);
+        t.it1 = static_cast<int>(static_cast<long long>(total) * (t.split + 1) / p.splits);
+    }
     return t;
+}
+
+// Number of k-iterations of a unit; the only thing the MMA issuer and the split warps need to know.
+__device__ __forceinline__ int unit_iters(const KParams &p, int unit) {
+    const int total = p.fold * p.kiters;
+    if (p.splits == 1) return total;
+    const int split = unit % p.splits;
+    return static_cast<int>(static_cast<long long>(total) * (split + 1) / p.splits) -
+           static_cast<int>(static_cast<long long>(total) * split / p.splits);
 }
 
 __device__ __forceinline__ void batch_coords(int q, int cnt, int d1, int d2, int &c0, int &c1, int &c2) {
@@ -186,15 +227,37 @@ __device__ __forceinline__ void batch_coords(int q, int cnt, int d1, int d2, int
     c0 = r / d1;
 }
 
+// Issues the TMA copies of one operand tile.  row0 = first row of the tile, nchunk = tile rows / 32.
+__device__ __forceinline__ void load_operand(int mode, uint32_t dst, const CUtensorMap *map, uint32_t bar, int k0,
+                                             int row0, int nchunk, uint32_t chunk_bytes, int c0, int c1, int c2) {
+    if (mode == kKMajor) {
+        tma_load_5d(dst, map, bar, k0, row0, c2, c1, c0);
+    } else if (mode == kMnSingleBox) {
+        tma_load_5d(dst, map, bar, 0, k0, row0 >> 5, c2, c1);
+    } else {
+        for (int c = 0; c < nchunk; ++c) tma_load_5d(dst + c * chunk_bytes, map, bar, row0 + c * 32, k0, c2, c1, c0);
+    }
+}
+
+template <int BN, int BK, bool FAST>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const KParams p) {
+               const __grid_constant__ CUtensorMap tmC, const KParams p) {
+    constexpr uint32_t A_BYTES = BM * BK * 4;
+    constexpr uint32_t B_BYTES = BN * BK * 4;
+    constexpr uint32_t RAW_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t STAGE_BYTES = FAST ? RAW_BYTES : 2 * RAW_BYTES;
+    constexpr uint32_t STAGE16 = STAGE_BYTES >> 4;
+    constexpr uint32_t LO16 = RAW_BYTES >> 4;              // lo copy of the stage, 16-byte units
+    constexpr int KSTEPS = BK / 8;
+    constexpr uint32_t TMEM_COLS = 2 * BN;                 // 128 / 256 / 512: double-buffered accumulator
+
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                 ~static_cast<uintptr_t>(1023));
     uint8_t *stage_base = smem;
-    float *epi_stage = reinterpret_cast<float *>(smem + static_cast<size_t>(p.stages) * p.stage_bytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(epi_stage) + kEpiBytes);
+    uint8_t *epi_base = smem + static_cast<size_t>(p.stages) * STAGE_BYTES;      // 1024-aligned
+    uint64_t *bars = reinterpret_cast<uint64_t *>(epi_base + kEpiBytes);
     // bars: full[S] | xform[S] | empty[S] | acc_full[2] | acc_empty[2]
     const uint32_t bar_full = smem_u32(bars);
     const uint32_t bar_xform = bar_full + 8u * kMaxStages;
@@ -206,7 +269,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const uint32_t tmem_cols = static_cast<uint32_t>(2 * p.bn);   // 128 / 256 / 512
+    const long long t_kernel0 = clock64();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
@@ -225,7 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(tmem_slot)),
-                     "r"(tmem_cols)
+                     "r"(TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -243,37 +306,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t phase = 0;
             int armed = 0;
             bool ok = true;
-            const uint32_t tx = p.a_bytes + p.b_bytes;
-            const uint32_t a_chunk = 128u * p.bk;   // bytes of one 32-wide MN chunk
+            long long waited = 0;
+            constexpr uint32_t CHUNK_BYTES = 128u * BK;   // one 32-wide MN chunk: BK k-rows of 128 bytes
+            const uint32_t dstA0 = smem_u32(stage_base);
+            uint32_t dstA = dstA0;
             for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
                 const TileCoord t = decode_unit(p, unit);
+                int f = 0, kk = t.it0;
+                if (p.fold > 1 || p.splits > 1) {
+                    f = t.it0 / p.kiters;
+                    kk = t.it0 - f * p.kiters;
+                }
+                int a0, a1, a2, b0, b1, b2;
+                batch_coords(t.bt * p.fold + f, p.a_batch, p.a_d1, p.a_d2, a0, a1, a2);
+                batch_coords(t.bt * p.fold + f, p.b_batch, p.b_d1, p.b_d2, b0, b1, b2);
+                const int rowA = t.tm * BM, rowB = t.tn * BN;
                 for (int it = t.it0; it < t.it1; ++it) {
-                    ok = mbar_wait(bar_empty + 8u * stage, phase ^ 1u, abort_flag, p.err, 0x100u | stage);
+                    ok = mbar_wait(bar_empty + 8u * stage, phase ^ 1u, abort_flag, p.err, 0x100u | stage, waited);
                     if (!ok) break;
                     const uint32_t full = bar_full + 8u * stage;
-                    mbar_arrive_expect_tx(full, tx);
+                    mbar_arrive_expect_tx(full, RAW_BYTES);
                     ++armed;
-                    const int f = it / p.kiters;
-                    const int k0 = (it - f * p.kiters) * p.bk;
-                    const int q = t.bt * p.fold + f;
-                    const uint32_t dstA = smem_u32(stage_base + static_cast<size_t>(stage) * p.stage_bytes);
-                    const uint32_t dstB = dstA + p.a_bytes;
-                    int c0, c1, c2;
-                    batch_coords(q, p.a_batch, p.a_d1, p.a_d2, c0, c1, c2);
-                    if (p.a_kmajor) {
-                        tma_load_5d(dstA, &tmA, full, k0, t.tm * BM, c2, c1, c0);
-                    } else {
-                        for (int c = 0; c < BM / 32; ++c)
-                            tma_load_5d(dstA + c * a_chunk, &tmA, full, t.tm * BM + c * 32, k0, c2, c1, c0);
+                    const int k0 = kk * BK;
+                    load_operand(p.a_mode, dstA, &tmA, full, k0, rowA, BM / 32, CHUNK_BYTES, a0, a1, a2);
+                    load_operand(p.b_mode, dstA + A_BYTES, &tmB, full, k0, rowB, BN / 32, CHUNK_BYTES, b0, b1, b2);
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; dstA = dstA0; } else { dstA += STAGE_BYTES; }
+                    if (++kk == p.kiters) {
+                        kk = 0;
+                        ++f;
+                        if (p.fold > 1) {
+                            batch_coords(t.bt * p.fold + f, p.a_batch, p.a_d1, p.a_d2, a0, a1, a2);
+                            batch_coords(t.bt * p.fold + f, p.b_batch, p.b_d1, p.b_d2, b0, b1, b2);
+                        }
                     }
-                    batch_coords(q, p.b_batch, p.b_d1, p.b_d2, c0, c1, c2);
-                    if (p.b_kmajor) {
-                        tma_load_5d(dstB, &tmB, full, k0, t.tn * p.bn, c2, c1, c0);
-                    } else {
-                        for (int c = 0; c < p.bn / 32; ++c)
-                            tma_load_5d(dstB + c * a_chunk, &tmB, full, t.tn * p.bn + c * 32, k0, c2, c1, c0);
-                    }
-                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok) {
@@ -285,6 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     while (!mbar_try_wait(bar_full + 8u * stage, phase) && clock64() - t0 < kWaitCycles / 8) {}
                 }
             }
+            if (p.prof) atomicAdd(p.prof + 0, static_cast<unsigned long long>(waited));
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -293,170 +359,201 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t phase = 0;
             int acc_it = 0;
             bool ok = true;
-            const int ksteps = p.bk / 8;
-            const uint32_t lo_off = (p.a_bytes + p.b_bytes) >> 4;   // lo copy of the stage, 16-byte units
+            long long waited = 0, waited_acc = 0;
+            const uint32_t sa0 = smem_u32(stage_base);
+            const uint32_t a_lo0 = ((sa0 >> 4) & 0x3FFFu) | p.a_desc_lbo;
+            const uint32_t b_lo0 = (((sa0 + A_BYTES) >> 4) & 0x3FFFu) | p.b_desc_lbo;
+            uint32_t a_lo = a_lo0, b_lo = b_lo0;
+            const uint32_t a_hi = p.a_desc_hi, b_hi = p.b_desc_hi;
+            const uint32_t a_ks = p.a_kstep, b_ks = p.b_kstep;
+            const uint32_t idesc = p.idesc;
+            const uint32_t ready0 = FAST ? bar_full : bar_xform;
             for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
-                const TileCoord t = decode_unit(p, unit);
+                const int iters = unit_iters(p, unit);
                 const int buf = acc_it & 1;
                 const uint32_t acc_phase = (acc_it >> 1) & 1;
-                ok = mbar_wait(bar_acc_empty + 8u * buf, acc_phase ^ 1u, abort_flag, p.err, 0x200u | buf);
+                ok = mbar_wait(bar_acc_empty + 8u * buf, acc_phase ^ 1u, abort_flag, p.err, 0x200u | buf, waited_acc);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.bn);
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
                 uint32_t accumulate = 0;
-                for (int it = t.it0; it < t.it1; ++it) {
-                    const uint32_t ready = (p.fast ? bar_full : bar_xform) + 8u * stage;
-                    ok = mbar_wait(ready, phase, abort_flag, p.err, 0x300u | stage);
+                for (int it = 0; it < iters; ++it) {
+                    ok = mbar_wait(ready0 + 8u * stage, phase, abort_flag, p.err, 0x300u | stage, waited);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(stage_base + static_cast<size_t>(stage) * p.stage_bytes);
-                    const uint32_t a_lo32 = ((sa >> 4) & 0x3FFFu) | p.a_desc_lbo;
-                    const uint32_t b_lo32 = (((sa + p.a_bytes) >> 4) & 0x3FFFu) | p.b_desc_lbo;
-                    for (int ks = 0; ks < ksteps; ++ks) {
-                        const uint64_t a_hi = p.a_desc_hi | (a_lo32 + ks * p.a_kstep);
-                        const uint64_t b_hi = p.b_desc_hi | (b_lo32 + ks * p.b_kstep);
-                        if (p.fast) {
-                            umma_tf32(d_tmem, a_hi, b_hi, p.idesc, accumulate);
+#pragma unroll
+                    for (int ks = 0; ks < KSTEPS; ++ks) {
+                        const uint32_t ak = a_lo + ks * a_ks, bk = b_lo + ks * b_ks;
+                        if (FAST) {
+                            umma_tf32(d_tmem, ak, a_hi, bk, b_hi, idesc, accumulate);
                         } else {
-                            const uint64_t a_lo = a_hi + lo_off;
-                            const uint64_t b_lo = b_hi + lo_off;
-                            umma_tf32(d_tmem, a_lo, b_hi, p.idesc, accumulate);
-                            umma_tf32(d_tmem, a_hi, b_lo, p.idesc, 1u);
-                            umma_tf32(d_tmem, a_hi, b_hi, p.idesc, 1u);
+                            umma_tf32(d_tmem, ak + LO16, a_hi, bk, b_hi, idesc, accumulate);
+                            umma_tf32(d_tmem, ak, a_hi, bk + LO16, b_hi, idesc, 1u);
+                            umma_tf32(d_tmem, ak, a_hi, bk, b_hi, idesc, 1u);
                         }
                         accumulate = 1u;
                     }
                     umma_commit(bar_empty + 8u * stage);
-                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                    if (++stage == p.stages) {
+                        stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0;
+                    } else {
+                        a_lo += STAGE16; b_lo += STAGE16;
+                    }
                 }
                 if (!ok) break;
                 umma_commit(bar_acc_full + 8u * buf);
                 ++acc_it;
             }
+            if (p.prof) {
+                atomicAdd(p.prof + 1, static_cast<unsigned long long>(waited_acc));
+                atomicAdd(p.prof + 2, static_cast<unsigned long long>(waited));
+            }
         }
     } else if (warp < 6) {
         // ------------------------------------------------------------ hi/lo split
-        if (!p.fast) {
+        if (!FAST) {
             const int tid = threadIdx.x - 64;
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            const int n4 = static_cast<int>((p.a_bytes + p.b_bytes) >> 4);
+            long long waited = 0;
+            constexpr int N4 = RAW_BYTES >> 4;            // float4 count of the raw stage
+            constexpr int PER = N4 / 128;                 // per thread
+            constexpr int U = (PER % 4 == 0) ? 4 : 2;
+            static_assert(N4 % 128 == 0 && PER % U == 0, "stage size must divide over the split warps");
             for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
-                const TileCoord t = decode_unit(p, unit);
-                for (int it = t.it0; it < t.it1; ++it) {
-                    ok = mbar_wait(bar_full + 8u * stage, phase, abort_flag, p.err, 0x400u | stage);
+                const int iters = unit_iters(p, unit);
+                for (int it = 0; it < iters; ++it) {
+                    ok = mbar_wait(bar_full + 8u * stage, phase, abort_flag, p.err, 0x400u | stage, waited);
                     if (!ok) break;
-                    float4 *raw = reinterpret_cast<float4 *>(stage_base + static_cast<size_t>(stage) * p.stage_bytes);
-                    float4 *lo = raw + n4;
-#pragma unroll 4
-                    for (int i = tid; i < n4; i += 128) {
-                        // The tensor core reads only the TF32 bits of a 32-bit operand (the low 13
-                        // mantissa bits are ignored), so the landed tile already is "hi"; only the
-                        // residual lo = x - trunc(x), exact in f32, has to be written.
-                        const float4 v = raw[i];
-                        float4 l;
-                        l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
-                        l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-                        l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
-                        l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-                        lo[i] = l;
+                    const float4 *raw = reinterpret_cast<const float4 *>(stage_base + static_cast<size_t>(stage) * STAGE_BYTES);
+                    float4 *lo = const_cast<float4 *>(raw) + N4;
+#pragma unroll
+                    for (int g = 0; g < PER; g += U) {
+                        float4 v[U];
+#pragma unroll
+                        for (int u = 0; u < U; ++u) v[u] = raw[tid + (g + u) * 128];
+#pragma unroll
+                        for (int u = 0; u < U; ++u) {
+                            float4 l;
+                            l.x = v[u].x - __uint_as_float(__float_as_uint(v[u].x) & 0xFFFFE000u);
+                            l.y = v[u].y - __uint_as_float(__float_as_uint(v[u].y) & 0xFFFFE000u);
+                            l.z = v[u].z - __uint_as_float(__float_as_uint(v[u].z) & 0xFFFFE000u);
+                            l.w = v[u].w - __uint_as_float(__float_as_uint(v[u].w) & 0xFFFFE000u);
+                            lo[tid + (g + u) * 128] = l;
+                        }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     mbar_arrive(bar_xform + 8u * stage);
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
             }
+            if (p.prof && tid == 0) atomicAdd(p.prof + 3, static_cast<unsigned long long>(waited));
         }
     } else {
         // ------------------------------------------------------------ epilogue
         const int q = warp & 3;                       // TMEM lane quarter this warp may read
-        float *stg = epi_stage + (warp - 6) * 32 * kEpiPitch;
+        uint8_t *my_stage = epi_base + (warp - 6) * 2 * kEpiBufBytes;
         int acc_it = 0;
+        int patch = 0;                                // staging buffer to use next
+        int in_flight = 0;                            // bulk groups committed by lane 0 and not yet waited for
         bool ok = true;
-        const bool vec_ok = ((p.ldc & 3) == 0) && ((p.c_bstride & 3) == 0) &&
-                            ((reinterpret_cast<uintptr_t>(p.splits > 1 ? p.partial : p.C) & 15) == 0) &&
-                            (p.splits == 1 || (p.N & 3) == 0);
+        long long waited = 0;
+        const bool use_tma = p.epi_mode != kEpiPlainStores;
+        const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
         for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
             const TileCoord t = decode_unit(p, unit);
             const int buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
-            ok = mbar_wait(bar_acc_full + 8u * buf, acc_phase, abort_flag, p.err, 0x500u | buf);
+            ok = mbar_wait(bar_acc_full + 8u * buf, acc_phase, abort_flag, p.err, 0x500u | buf, waited);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            float *out;
-            long long ld;
-            if (p.splits > 1) {
-                ld = p.N;
-                out = p.partial + (static_cast<long long>(t.split) * p.batch + t.bt) * p.M * ld;
-            } else {
-                ld = p.ldc;
-                out = p.C + static_cast<long long>(t.bt) * p.c_bstride;
-            }
             const bool fuse = p.splits == 1;
-            const int row_base = t.tm * BM + q * 32;
-            const int rsub = lane >> 3;               // 0..3
-            const int c4 = (lane & 7) * 4;            // 0,4,..,28
-            for (int chunk = 0; chunk < p.bn / 32; ++chunk) {
-                const int col0 = t.tn * p.bn + chunk * 32;
-                if (col0 >= p.N) break;               // warp-uniform
-                uint32_t v[32];
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                       static_cast<uint32_t>(buf * p.bn + chunk * 32);
-                tmem_ld32(taddr, v);
-                float4 *srow = reinterpret_cast<float4 *>(stg + lane * kEpiPitch);
+            const int row0 = t.tm * BM + q * 32;
+            const int cbatch = fuse ? t.bt : t.split * p.batch + t.bt;
+            const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
+            if (row0 < p.M) {
+                for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                    const int col0 = t.tn * BN + chunk * 32;
+                    if (col0 >= p.N) break;           // warp-uniform
+                    uint32_t v[32];
+                    tmem_ld32_issue(tbase + chunk * 32, v);
+                    tmem_ld_wait();
+                    if (fuse && p.bias != nullptr) {
+                        if (bias_vec && col0 + 32 <= p.N) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    srow[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                          __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                __syncwarp();
-                const int col = col0 + c4;
-                float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (fuse && p.bias != nullptr) {
-                    if (col + 0 < p.N) bv.x = __ldg(p.bias + col + 0);
-                    if (col + 1 < p.N) bv.y = __ldg(p.bias + col + 1);
-                    if (col + 2 < p.N) bv.z = __ldg(p.bias + col + 2);
-                    if (col + 3 < p.N) bv.w = __ldg(p.bias + col + 3);
-                }
+                            for (int j = 0; j < 8; ++j) {
+                                const float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + col0) + j);
+                                v[4 * j + 0] = __float_as_uint(__uint_as_float(v[4 * j + 0]) + b.x);
+                                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + b.y);
+                                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + b.z);
+                                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + b.w);
+                            }
+                        } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int r = i * 4 + rsub;
-                    const int row = row_base + r;
-                    if (row >= p.M || col >= p.N) continue;
-                    float4 x = *reinterpret_cast<const float4 *>(stg + r * kEpiPitch + c4);
-                    x.x += bv.x; x.y += bv.y; x.z += bv.z; x.w += bv.w;
-                    float *dst = out + static_cast<long long>(row) * ld + col;
-                    if (vec_ok && col + 3 < p.N) {
-                        if (fuse && p.accumulate) {
-                            const float4 o = *reinterpret_cast<const float4 *>(dst);
-                            x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.N) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldg(p.bias + col0 + j));
                         }
-                        *reinterpret_cast<float4 *>(dst) = x;
+                    }
+                    if (use_tma) {
+                        // The patch about to be overwritten must have been read by its TMA store.
+                        if (lane == 0 && in_flight == 2) {
+                            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                            in_flight = 1;
+                        }
+                        __syncwarp();
+                        uint8_t *dst = my_stage + patch * kEpiBufBytes + lane * 128;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            *reinterpret_cast<float4 *>(dst + ((j ^ (lane & 7)) << 4)) =
+                                make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                            __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            const uint32_t src = smem_u32(my_stage + patch * kEpiBufBytes);
+                            if (p.epi_mode == kEpiTmaReduce && fuse) tma_reduce_add_5d(&tmC, src, col0, row0, cbatch);
+                            else tma_store_5d(&tmC, src, col0, row0, cbatch);
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            ++in_flight;
+                        }
+                        patch ^= 1;
                     } else {
-                        const float xs[4] = {x.x, x.y, x.z, x.w};
-                        for (int e = 0; e < 4; ++e) {
-                            if (col + e < p.N) {
-                                float y = xs[e];
-                                if (fuse && p.accumulate) y += dst[e];
-                                dst[e] = y;
+                        const int row = row0 + lane;
+                        if (row < p.M) {
+                            float *out = fuse ? p.C + static_cast<long long>(t.bt) * p.c_bstride + static_cast<long long>(row) * p.ldc
+                                              : p.partial + (static_cast<long long>(cbatch) * p.M + row) * p.N;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (col0 + j < p.N) {
+                                    float y = __uint_as_float(v[j]);
+                                    if (fuse && p.accumulate) y += out[col0 + j];
+                                    out[col0 + j] = y;
+                                }
                             }
                         }
                     }
                 }
-                __syncwarp();
             }
             tc_fence_before();
             mbar_arrive(bar_acc_empty + 8u * buf);
             ++acc_it;
         }
+        if (use_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (p.prof && warp == 6 && lane == 0) atomicAdd(p.prof + 4, static_cast<unsigned long long>(waited));
     }
 
     tc_fence_before();
     __syncthreads();
+    if (p.prof && threadIdx.x == 0) {
+        atomicAdd(p.prof + 5, static_cast<unsigned long long>(clock64() - t_kernel0));
+        atomicAdd(p.prof + 6, 1ull);
+    }
     if (warp == 1) {
+        __syncwarp();
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
                      : "memory");
     }
 }
@@ -506,13 +603,52 @@ int env_int(const char *name, int dflt) {
     return v && *v ? atoi(v) : dflt;
 }
 
-int make_map(CUtensorMap *map, const Operand &op, int box_rows, int bk) {
-    EncodeTiledFn enc = encode_fn();
-    if (!enc) return fail(MNI_B200_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+CUresult encode(CUtensorMap *map, const float *ptr, const cuuint64_t *dims, const cuuint64_t *strides,
+                const cuuint32_t *box, CUtensorMapSwizzle swz) {
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(ptr), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
+// Builds the tensor map of one operand and reports the OperandMode the kernel must use for it.
+int make_operand_map(CUtensorMap *map, const Operand &op, int box_rows, int bk, int *mode) {
+    if (!encode_fn()) return fail(MNI_B200_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
     cuuint64_t dims[5];
     cuuint64_t strides[4];   // bytes, dims 1..4
     cuuint32_t box[5] = {1, 1, 1, 1, 1};
-    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    // A size-1 dim never advances, but its stride must still be a positive multiple of 16 bytes.
+    uint64_t span = 16;
+    auto stride_or = [&](int64_t extent, int64_t stride_elems) -> cuuint64_t {
+        return static_cast<cuuint64_t>((extent > 1 && stride_elems > 0) ? static_cast<uint64_t>(stride_elems) * 4u : span);
+    };
+    // 32-bit elements read MN-major by the tensor core use the 128-byte swizzle whose unit is a
+    // 32-byte chunk, not the usual 16-byte chunk.
+    const CUtensorMapSwizzle mn_swz = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+    if (!op.k_major && op.rows % 32 == 0 && op.bshape[0] == 1 && env_int("MNI_B200_NO_SINGLE_BOX", 0) == 0) {
+        // One box per tile: the MN dim is split into (32 contiguous floats, rows/32 chunks), giving the
+        // smem order [chunk][k][32 floats] the MMA descriptor expects.
+        dims[0] = 32;
+        dims[1] = static_cast<cuuint64_t>(op.kdim);
+        dims[2] = static_cast<cuuint64_t>(op.rows / 32);
+        dims[3] = static_cast<cuuint64_t>(op.bshape[2]);
+        dims[4] = static_cast<cuuint64_t>(op.bshape[1]);
+        span = 128;
+        strides[0] = stride_or(op.kdim, op.ld);
+        span = std::max<uint64_t>(span, strides[0] * dims[1]);
+        strides[1] = 128;
+        strides[2] = stride_or(op.bshape[2], op.bstride[2]);
+        span = std::max<uint64_t>(span, strides[2] * dims[3]);
+        strides[3] = stride_or(op.bshape[1], op.bstride[1]);
+        box[0] = 32;
+        box[1] = static_cast<cuuint32_t>(bk);
+        box[2] = static_cast<cuuint32_t>(box_rows / 32);
+        if (encode(map, op.ptr, dims, strides, box, mn_swz) == CUDA_SUCCESS) {
+            *mode = kMnSingleBox;
+            return MNI_B200_OK;
+        }
+        box[2] = 1;   // fall through to the multi-box form
+    }
     CUtensorMapSwizzle swz;
     if (op.k_major) {
         dims[0] = static_cast<cuuint64_t>(op.kdim);
@@ -520,22 +656,15 @@ int make_map(CUtensorMap *map, const Operand &op, int box_rows, int bk) {
         box[0] = static_cast<cuuint32_t>(bk);
         box[1] = static_cast<cuuint32_t>(box_rows);
         swz = bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+        *mode = kKMajor;
     } else {
         dims[0] = static_cast<cuuint64_t>(op.rows);
         dims[1] = static_cast<cuuint64_t>(op.kdim);
         box[0] = 32;
         box[1] = static_cast<cuuint32_t>(bk);
-        // 32-bit elements read MN-major by the tensor core use the 128-byte swizzle whose unit
-        // is a 32-byte chunk (8 k-steps' worth of one row pair), not the usual 16-byte chunk.
-        swz = static_cast<CUtensorMapSwizzle>(env_int("MNI_B200_DEBUG_MN_TMA_SWIZZLE",
-                                                      static_cast<int>(CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)));
+        swz = mn_swz;
+        *mode = kMnMultiBox;
     }
-    // A size-1 dim never advances, but its stride must still be a positive multiple of 16 bytes.
-    uint64_t span = 16;
-    auto stride_or = [&](int64_t extent, int64_t stride_elems) -> cuuint64_t {
-        uint64_t s = (extent > 1 && stride_elems > 0) ? static_cast<uint64_t>(stride_elems) * 4u : span;
-        return static_cast<cuuint64_t>(s);
-    };
     span = std::max<uint64_t>(16, (static_cast<uint64_t>(dims[0]) * 4u + 15u) & ~15ull);
     strides[0] = stride_or(static_cast<int64_t>(dims[1]), op.ld);
     span = std::max<uint64_t>(span, strides[0] * dims[1]);
@@ -545,9 +674,7 @@ int make_map(CUtensorMap *map, const Operand &op, int box_rows, int bk) {
         strides[1 + i] = stride_or(op.bshape[bi], op.bstride[bi]);
         span = std::max<uint64_t>(span, strides[1 + i] * dims[2 + i]);
     }
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(op.ptr), dims, strides, box,
-                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = encode(map, op.ptr, dims, strides, box, swz);
     if (r != CUDA_SUCCESS)
         return fail(MNI_B200_ERR_CUDA,
                     "cuTensorMapEncodeTiled failed (%d): dims %llu x %llu, ld %lld, k_major %d", static_cast<int>(r),
@@ -556,10 +683,26 @@ int make_map(CUtensorMap *map, const Operand &op, int box_rows, int bk) {
     return MNI_B200_OK;
 }
 
+// Tensor map of the output (or of the split-K partial buffer): dims (N, M, batches), 32 x 32 boxes.
+int make_output_map(CUtensorMap *map, float *ptr, int64_t N, int64_t M, int64_t batches, int64_t ld, int64_t bstride) {
+    cuuint64_t dims[5] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(batches), 1, 1};
+    cuuint64_t strides[4];
+    strides[0] = static_cast<cuuint64_t>(M > 1 ? ld * 4 : ((N * 4 + 15) & ~15LL));
+    strides[1] = static_cast<cuuint64_t>(batches > 1 ? bstride * 4 : std::max<int64_t>(strides[0] * M, 16));
+    strides[2] = strides[1] * static_cast<cuuint64_t>(batches);
+    strides[3] = strides[2];
+    const cuuint32_t box[5] = {32, 32, 1, 1, 1};
+    const CUresult r = encode(map, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != CUDA_SUCCESS) return fail(MNI_B200_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed (%d)", static_cast<int>(r));
+    return MNI_B200_OK;
+}
+
 struct Plan {
     int bn, bk, stages, splits, tiles_m, tiles_n, grid;
     size_t smem;
 };
+
+constexpr size_t kFixedSmem = 1024 + kEpiBytes + kBarBytes;
 
 Plan make_plan(const GemmProblem &p, int sm_count) {
     Plan pl;
@@ -571,12 +714,11 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     if (bk_env == 16 || bk_env == 32) pl.bk = bk_env;
     const size_t raw = static_cast<size_t>(BM + pl.bn) * pl.bk * 4;
     const size_t stage = p.fast_tf32 ? raw : 2 * raw;
-    const size_t fixed = 1024 + kEpiBytes + (3 * kMaxStages + 4) * 8 + 16;
     const size_t budget = 227 * 1024;
-    pl.stages = static_cast<int>(std::min<size_t>(kMaxStages, (budget - fixed) / stage));
+    pl.stages = static_cast<int>(std::min<size_t>(kMaxStages, (budget - kFixedSmem) / stage));
     const int st_env = env_int("MNI_B200_STAGES", 0);
     if (st_env >= 1 && st_env <= pl.stages) pl.stages = st_env;
-    pl.smem = fixed + static_cast<size_t>(pl.stages) * stage;
+    pl.smem = kFixedSmem + static_cast<size_t>(pl.stages) * stage;
     pl.tiles_m = static_cast<int>((p.M + BM - 1) / BM);
     pl.tiles_n = static_cast<int>((p.N + pl.bn - 1) / pl.bn);
     const long long tiles = static_cast<long long>(p.batch) * pl.tiles_m * pl.tiles_n;
@@ -595,12 +737,51 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     return pl;
 }
 
-uint64_t desc_hi_bits(uint32_t sbo_bytes, uint32_t layout_type) {
-    return (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) |
-           (static_cast<uint64_t>(layout_type) << 61);
+uint32_t desc_hi_bits(uint32_t sbo_bytes, uint32_t layout_type) {
+    // upper word of the shared-memory descriptor: SBO [32,46) | version 1 [46,48) | layout [61,64)
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (layout_type << 29);
+}
+
+template <int BN, int BK, bool FAST>
+cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
+                           const KParams &k, cudaStream_t stream) {
+    static std::once_flag once;
+    static cudaError_t attr = cudaSuccess;
+    std::call_once(once, [] {
+        attr = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    });
+    if (attr != cudaSuccess) return attr;
+    gemm_tc_kernel<BN, BK, FAST><<<pl.grid, kThreads, pl.smem, stream>>>(tmA, tmB, tmC, k);
+    return cudaSuccess;
 }
 
 }  // namespace
+
+// Role wait counters (diagnostics): cycles summed over CTAs that each role spent blocked.
+__device__ unsigned long long g_role_waits[8];
+
+unsigned long long *role_wait_ptr() {
+    static thread_local int cached_dev = -1;
+    static thread_local unsigned long long *ptr = nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    if (dev != cached_dev) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_role_waits) != cudaSuccess) return nullptr;
+        ptr = static_cast<unsigned long long *>(p);
+        cached_dev = dev;
+    }
+    return ptr;
+}
+
+int read_role_waits(uint64_t out[8], int reset) {
+    unsigned long long *ptr = role_wait_ptr();
+    if (!ptr) return fail(MNI_B200_ERR_CUDA, "role wait counters unavailable");
+    MNI_CUDA(cudaDeviceSynchronize());
+    MNI_CUDA(cudaMemcpy(out, ptr, 8 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    if (reset) MNI_CUDA(cudaMemset(ptr, 0, 8 * sizeof(uint64_t)));
+    return MNI_B200_OK;
+}
 
 size_t gemm_tc_partial_bytes(const GemmProblem &p, int sm_count) {
     const Plan pl = make_plan(p, sm_count);
@@ -612,25 +793,33 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
                    cudaStream_t stream) {
     if (p.M <= 0 || p.N <= 0 || p.batch <= 0) return MNI_B200_OK;
     const Plan pl = make_plan(p, sm_count);
-    if (p.K <= 0) {
-        // Empty contraction: the product is all zeros (ops/matmul.rs:48 starts from a zeroed output).
-        return fail(MNI_B200_ERR_ARG, "empty contraction reached the tensor-core launcher");
-    }
-    static std::once_flag attr_once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once, [] {
-        attr_err = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    });
-    if (attr_err != cudaSuccess)
-        return fail(MNI_B200_ERR_CUDA, "cudaFuncSetAttribute(smem) failed: %s", cudaGetErrorString(attr_err));
-
-    CUtensorMap tmA, tmB;
-    int rc = make_map(&tmA, p.A, BM, pl.bk);
-    if (rc) return rc;
-    rc = make_map(&tmB, p.B, pl.bn, pl.bk);
-    if (rc) return rc;
+    if (p.K <= 0) return fail(MNI_B200_ERR_ARG, "empty contraction reached the tensor-core launcher");
+    if (pl.splits > 1 && partial == nullptr)
+        return fail(MNI_B200_ERR_WORKSPACE, "split-K launch without partial storage");
 
     KParams k{};
+    CUtensorMap tmA, tmB, tmC;
+    int rc = make_operand_map(&tmA, p.A, BM, pl.bk, &k.a_mode);
+    if (rc) return rc;
+    rc = make_operand_map(&tmB, p.B, pl.bn, pl.bk, &k.b_mode);
+    if (rc) return rc;
+
+    // Epilogue: TMA store when the destination rows are 16-byte aligned, plain stores otherwise.
+    float *dst = pl.splits > 1 ? partial : p.C;
+    const int64_t dst_ld = pl.splits > 1 ? p.N : p.ldc;
+    const int64_t dst_bs = pl.splits > 1 ? p.M * p.N : p.c_bstride;
+    const int64_t dst_batches = pl.splits > 1 ? static_cast<int64_t>(pl.splits) * p.batch : p.batch;
+    const bool tma_ok = (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && dst_ld % 4 == 0 && dst_bs % 4 == 0 &&
+                        env_int("MNI_B200_NO_TMA_STORE", 0) == 0;
+    k.epi_mode = kEpiPlainStores;
+    if (tma_ok) {
+        rc = make_output_map(&tmC, dst, p.N, p.M, dst_batches, dst_ld, dst_bs);
+        if (rc) return rc;
+        k.epi_mode = (p.accumulate && pl.splits == 1) ? kEpiTmaReduce : kEpiTmaStore;
+    } else {
+        tmC = tmA;   // unused by the plain-store epilogue, but must be a valid object
+    }
+
     k.M = static_cast<int>(p.M);
     k.N = static_cast<int>(p.N);
     k.tiles_m = pl.tiles_m;
@@ -646,26 +835,17 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     k.b_batch = static_cast<int>(p.B.batch);
     k.b_d1 = static_cast<int>(p.B.bshape[1]);
     k.b_d2 = static_cast<int>(p.B.bshape[2]);
-    k.a_kmajor = p.A.k_major;
-    k.b_kmajor = p.B.k_major;
-    k.bn = pl.bn;
-    k.bk = pl.bk;
     k.stages = pl.stages;
-    k.fast = p.fast_tf32;
     k.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.A.k_major ? 0u : 1u) << 15) |
               ((p.B.k_major ? 0u : 1u) << 16) | (static_cast<uint32_t>(pl.bn >> 3) << 17) |
               (static_cast<uint32_t>(BM >> 4) << 24);
-    k.a_bytes = static_cast<uint32_t>(BM * pl.bk * 4);
-    k.b_bytes = static_cast<uint32_t>(pl.bn * pl.bk * 4);
-    k.stage_bytes = (k.a_bytes + k.b_bytes) * (p.fast_tf32 ? 1u : 2u);
     // K-major tile: rows of BK floats, 8-row groups SBO apart, swizzle span = one row.
     // MN-major tile: 32-float chunks of BK k-rows (LBO apart); the 32-byte-unit swizzle repeats every
     // 4 k-rows (SBO = 512), and one 8-deep k-step spans two such groups (1024 bytes).
     const uint32_t k_layout = pl.bk == 32 ? 2u : 4u;   // SWIZZLE_128B : SWIZZLE_64B
     const uint32_t k_sbo = static_cast<uint32_t>(8 * pl.bk * 4);
-    const uint32_t mn_lbo = static_cast<uint32_t>(env_int("MNI_B200_DEBUG_MN_LBO", pl.bk * 128));
-    const uint32_t mn_sbo = static_cast<uint32_t>(env_int("MNI_B200_DEBUG_MN_SBO", 512));
-    const uint32_t mn_layout = static_cast<uint32_t>(env_int("MNI_B200_DEBUG_MN_LAYOUT", 1));   // SWIZZLE_128B_BASE32B
+    const uint32_t mn_lbo = static_cast<uint32_t>(pl.bk * 128);
+    const uint32_t mn_sbo = 512, mn_layout = 1;        // SWIZZLE_128B_BASE32B
     if (p.A.k_major) { k.a_desc_hi = desc_hi_bits(k_sbo, k_layout); k.a_desc_lbo = 0; k.a_kstep = 2; }
     else { k.a_desc_hi = desc_hi_bits(mn_sbo, mn_layout); k.a_desc_lbo = ((mn_lbo >> 4) & 0x3FFFu) << 16; k.a_kstep = 64; }
     if (p.B.k_major) { k.b_desc_hi = desc_hi_bits(k_sbo, k_layout); k.b_desc_lbo = 0; k.b_kstep = 2; }
@@ -677,10 +857,18 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     k.bias = p.bias;
     k.accumulate = p.accumulate;
     k.err = err_word;
-    if (pl.splits > 1 && partial == nullptr)
-        return fail(MNI_B200_ERR_WORKSPACE, "split-K launch without partial storage");
+    k.prof = env_int("MNI_B200_ROLE_WAITS", 0) ? role_wait_ptr() : nullptr;
 
-    gemm_tc_kernel<<<pl.grid, kThreads, pl.smem, stream>>>(tmA, tmB, k);
+    cudaError_t e = cudaErrorInvalidValue;
+#define MNI_VARIANT(BN_, BK_)                                                                         \
+    if (pl.bn == BN_ && pl.bk == BK_) {                                                               \
+        e = p.fast_tf32 ? launch_variant<BN_, BK_, true>(pl, tmA, tmB, tmC, k, stream)                \
+                        : launch_variant<BN_, BK_, false>(pl, tmA, tmB, tmC, k, stream);              \
+    }
+    MNI_VARIANT(64, 16) MNI_VARIANT(64, 32) MNI_VARIANT(128, 16) MNI_VARIANT(128, 32) MNI_VARIANT(256, 16)
+    MNI_VARIANT(256, 32)
+#undef MNI_VARIANT
+    if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "gemm_tc_kernel set-up failed: %s", cudaGetErrorString(e));
     MNI_LAUNCH_CHECK("gemm_tc_kernel");
     if (pl.splits > 1) {
         const long long total = static_cast<long long>(p.batch) * p.M * p.N;

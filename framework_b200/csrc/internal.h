@@ -79,6 +79,10 @@ size_t gemm_tc_partial_bytes(const GemmProblem &p, int sm_count);
 int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int sm_count,
                    cudaStream_t stream);
 
+// Diagnostics: copies the 8 role wait counters of the current device (collected only while
+// MNI_B200_ROLE_WAITS=1 is set in the environment) and optionally clears them.
+int read_role_waits(uint64_t out[8], int reset);
+
 // Skinny path (few output rows, HBM-bound): CUDA-core fp32 FMA kernels.
 //   y[M,N] = x[M,K] . W[K,N]          (W row-major, ldw)           M <= 16
 bool skinny_fwd_supported(int64_t M, int64_t N, int64_t K);

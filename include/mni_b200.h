@@ -174,6 +174,16 @@ MNI_B200_API int mni_b200_workspace_query(const mni_b200_view *a, const mni_b200
  */
 MNI_B200_API int mni_b200_device_status(void *stream, uint32_t *detail);
 
+/*
+ * Diagnostics for the tensor-core kernel.  While the environment variable
+ * MNI_B200_ROLE_WAITS=1 is set, every launch adds, summed over its CTAs, the clock cycles each
+ * warp role spent blocked: out[0] TMA producer waiting for a free stage, out[1] MMA issuer
+ * waiting for a free accumulator, out[2] MMA issuer waiting for operands, out[3] split warps
+ * waiting for TMA data, out[4] epilogue waiting for a finished accumulator, out[5] total CTA
+ * cycles, out[6] CTAs counted.  Synchronises the device.  (No counterpart in the reference.)
+ */
+MNI_B200_API int mni_b200_role_wait_cycles(uint64_t out[8], int reset);
+
 /* Number of kernels this library has launched in this process (all threads). */
 MNI_B200_API uint64_t mni_b200_launch_count(void);
 
