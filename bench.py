@@ -34,21 +34,24 @@ if ROOT not in sys.path:
 
 METRIC = "f32_matmul_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
-L2_BYTES = 126 * 1024 * 1024
 
 
 # --------------------------------------------------------------------------- workloads
 class Workload:
-    """Shapes, seeded synthetic inputs and the fwd+bwd call sequence of one configuration."""
+    """Shapes and seeded synthetic inputs of one configuration.
+
+    kind "gemm": y = a . b (+ bias); backward from dy gives da, db (, dbias).
+    kind "attention": S = q . k^T (k^T a stride-only permute view), O = S . v; backward from dO
+    gives dS, dV, dQ, dK^T -- the six GEMMs of the attention-shaped configuration.
+    """
 
     def __init__(self, name, desc, a_shape, b_shape, *, bias=False, b_perm=None, dist_a="normal",
-                 dist_b="normal", scale_b=1.0):
-        self.name, self.desc = name, desc
+                 scale_b=1.0, kind="gemm"):
+        self.name, self.desc, self.kind = name, desc, kind
         self.a_shape, self.b_shape = tuple(a_shape), tuple(b_shape)
         self.bias, self.b_perm = bias, b_perm
-        self.dist_a, self.dist_b, self.scale_b = dist_a, dist_b, scale_b
+        self.dist_a, self.scale_b = dist_a, scale_b
 
-    # logical shapes ----------------------------------------------------------
     @property
     def b_logical(self):
         return tuple(self.b_shape[d] for d in self.b_perm) if self.b_perm else self.b_shape
@@ -64,32 +67,50 @@ class Workload:
         return broadcast_shape(self.a_shape[:-2], self.b_logical[:-2]) + (m, n)
 
     @property
-    def flops(self):
-        """Algorithmic flops of forward + backward = 3 GEMMs of 2*M*N*K per output batch."""
-        m, k, n = self.mkn
-        batch = int(np.prod(self.out_shape[:-2])) if len(self.out_shape) > 2 else 1
-        return 3 * 2 * m * n * k * batch
+    def batch(self):
+        return int(np.prod(self.out_shape[:-2])) if len(self.out_shape) > 2 else 1
 
-    def host_inputs(self, seed=0):
+    @property
+    def flops(self):
+        """Algorithmic flops of forward + backward: 3 GEMMs of 2*M*N*K per batch (6 for attention)."""
+        m, k, n = self.mkn
+        one = 2 * m * n * k * self.batch
+        return 6 * one if self.kind == "attention" else 3 * one
+
+    @property
+    def fwd_flops(self):
+        return self.flops // 3
+
+    def host_inputs(self, seed=0) -> dict:
         rng = np.random.default_rng(seed)
 
-        def draw(shape, dist, scale):
-            if dist == "uniform":
-                return rng.random(shape, dtype=np.float32)
+        def normal(shape, scale=1.0):
             return (scale * rng.standard_normal(shape, dtype=np.float32)).astype(np.float32)
-        a = draw(self.a_shape, self.dist_a, 1.0)
-        b = draw(self.b_shape, self.dist_b, self.scale_b)
-        bias = draw((self.mkn[2],), "normal", 0.02) if self.bias else None
-        dy = draw(self.out_shape, "normal", 1.0)
-        return a, b, bias, dy
+        if self.kind == "attention":
+            return {"q": normal(self.a_shape), "k": normal(self.b_shape), "v": normal(self.a_shape),
+                    "do": normal(self.a_shape)}
+        a = rng.random(self.a_shape, dtype=np.float32) if self.dist_a == "uniform" else normal(self.a_shape)
+        out = {"a": a, "b": normal(self.b_shape, self.scale_b)}
+        if self.bias:
+            out["bias"] = normal((self.mkn[2],), 0.02)
+        out["dy"] = normal(self.out_shape)
+        return out
+
+    def with_a_shape(self, a_shape, note=""):
+        b_shape = self.b_shape
+        if self.kind == "attention" or (len(self.b_shape) == len(self.a_shape) and len(self.a_shape) > 2
+                                        and self.b_shape[0] == self.a_shape[0]):
+            b_shape = (a_shape[0],) + tuple(self.b_shape[1:])
+        return Workload(self.name, self.desc + note, a_shape, b_shape, bias=self.bias, b_perm=self.b_perm,
+                        dist_a=self.dist_a, scale_b=self.scale_b, kind=self.kind)
 
 
 WORKLOADS = {
     "c1": Workload("c1", "2-D A[512,512].B[512,512] ~N(0,1)", (512, 512), (512, 512)),
     "c2": Workload("c2", "Linear step x[4096,1024].W[1024,4096]+b[4096], dy~N(0,1)", (4096, 1024), (1024, 4096),
                    bias=True, dist_a="uniform", scale_b=0.02),
-    "c3": Workload("c3", "attention-shaped Q.K^T, K^T a permute(0,1,3,2) view of [8,12,512,64]",
-                   (8, 12, 512, 64), (8, 12, 512, 64), b_perm=(0, 1, 3, 2)),
+    "c3": Workload("c3", "attention-shaped Q,K,V [8,12,512,64]: S=Q.K^T (K^T a permute view), O=S.V, fwd+bwd",
+                   (8, 12, 512, 64), (8, 12, 512, 64), b_perm=(0, 1, 3, 2), kind="attention"),
     "c4": Workload("c4", "broadcast weight [64,1024,768].[768,3072], dW summed over the batch",
                    (64, 1024, 768), (768, 3072), scale_b=0.02),
     "c5a": Workload("c5a", "square 8192^3 ~N(0,1)", (8192, 8192), (8192, 8192)),
@@ -97,17 +118,57 @@ WORKLOADS = {
     "c5b4": Workload("c5b4", "skinny M=4, K=N=4096", (4, 4096), (4096, 4096)),
     "c5b16": Workload("c5b16", "skinny M=16, K=N=4096", (16, 4096), (4096, 4096)),
 }
+HBM_BOUND = ("c3", "c5b1", "c5b4", "c5b16")
 
 
-def shard_workload(wl: Workload, world: int) -> Workload:
+def shard_workload(wl: Workload, rank: int, world: int) -> Workload:
     """Per-rank shard for the configurations that partition: batch shards for c4, row shards for
     c5a.  c2 is weak-scaled (every rank owns a full-size batch shard), the rest run as replicas."""
     if world == 1 or wl.name not in ("c4", "c5a"):
         return wl
     from framework_b200.sharding import shard_leading
-    a_shape = shard_leading(wl.a_shape, int(os.environ.get("RANK", "0")), world)
-    return Workload(wl.name, wl.desc + f" (1/{world} shard)", a_shape, wl.b_shape, bias=wl.bias,
-                    b_perm=wl.b_perm, dist_a=wl.dist_a, dist_b=wl.dist_b, scale_b=wl.scale_b)
+    return wl.with_a_shape(shard_leading(wl.a_shape, rank, world), f" (1/{world} shard)")
+
+
+class Problem:
+    """Device-side instance of a workload: resident inputs, preallocated outputs, the call sequence."""
+
+    def __init__(self, F, wl: Workload, host: dict, dev, flags: int):
+        T = F.DeviceTensor
+        self.F, self.wl, self.flags = F, wl, flags
+        self.inp = {k: T.from_numpy(v, dev) for k, v in host.items()}
+        if wl.kind == "attention":
+            self.kt = self.inp["k"].permute(wl.b_perm)
+            shp = wl.out_shape
+            self.out = {"s": T.empty(shp, dev), "o": T.empty(wl.a_shape, dev), "ds": T.empty(shp, dev),
+                        "dv": T.empty(wl.a_shape, dev), "dq": T.empty(wl.a_shape, dev),
+                        "dkt": T.empty(self.kt.shape, dev)}
+        else:
+            self.b = self.inp["b"].permute(wl.b_perm) if wl.b_perm else self.inp["b"]
+            self.out = {"y": T.empty(wl.out_shape, dev), "da": T.empty(wl.a_shape, dev),
+                        "db": T.empty(self.b.shape, dev)}
+            if wl.bias:
+                self.out["dbias"] = T.empty((wl.mkn[2],), dev)
+
+    def forward(self):
+        F, i, o = self.F, self.inp, self.out
+        if self.wl.kind == "attention":
+            F.matmul(i["q"], self.kt, flags=self.flags, out=o["s"])
+            F.matmul(o["s"], i["v"], flags=self.flags, out=o["o"])
+        else:
+            F.matmul(i["a"], self.b, i.get("bias"), flags=self.flags, out=o["y"])
+
+    def backward(self):
+        F, i, o = self.F, self.inp, self.out
+        if self.wl.kind == "attention":
+            F.matmul_backward(i["do"], o["s"], i["v"], flags=self.flags, da=o["ds"], db=o["dv"])
+            F.matmul_backward(o["ds"], i["q"], self.kt, flags=self.flags, da=o["dq"], db=o["dkt"])
+        else:
+            F.matmul_backward(i["dy"], i["a"], self.b, flags=self.flags, da=o["da"], db=o["db"],
+                              dbias=o.get("dbias"), want_dbias=self.wl.bias)
+
+    def weight_grads(self):
+        return [self.out[k].storage for k in ("db", "dbias") if k in self.out]
 
 
 # --------------------------------------------------------------------------- clocks
@@ -124,7 +185,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
@@ -136,10 +197,10 @@ class ClockSampler:
     def stop(self, t0: float, t1: float) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
-        sm, smax, reasons = [], None, set()
-        rows = [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for _, l in self.lines]
+        sm, power, smax, reasons = [], [], None, set()
+        rows = [l for (t, l) in self.lines if t0 <= t <= t1 + 0.02] or [l for _, l in self.lines][-3:]
         for line in rows:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
@@ -147,13 +208,14 @@ class ClockSampler:
             try:
                 sm.append(float(f[1]))
                 smax = float(f[2])
+                power.append(float(f[3]))
             except ValueError:
                 continue
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -166,51 +228,45 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    if world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
     base = WORKLOADS[args.workload]
-    wl = shard_workload(base, world)
+    wl = shard_workload(base, rank, world)
     flags = F._lib.PRECISION_TF32 if args.precision == "tf32" else 0
-    a_np, b_np, bias_np, dy_np = wl.host_inputs(seed=rank)
-    if world > 1:   # the weight (and bias) are replicated
-        _, b_np, bias_np, _ = wl.host_inputs(seed=0)
-    T = F.DeviceTensor
-
-    def to_dev(x):
-        return T.from_numpy(x, dev) if x is not None else None
-    a, b, bias, dy = to_dev(a_np), to_dev(b_np), to_dev(bias_np), to_dev(dy_np)
-    if wl.b_perm:
-        b = b.permute(wl.b_perm)
-    y = T.empty(wl.out_shape, dev)
-    da, db = T.empty(a.shape, dev), T.empty(b.shape, dev)
-    dbias = T.empty((wl.mkn[2],), dev) if wl.bias else None
+    host = wl.host_inputs(seed=rank)
+    if world > 1 and wl.kind == "gemm":      # the weight (and bias) are replicated
+        shared = wl.host_inputs(seed=0)
+        for key in ("b", "bias"):
+            if key in host:
+                host[key] = shared[key]
+    prob = Problem(F, wl, host, dev, flags)
     reduce_grads = world > 1 and wl.name in ("c2", "c4", "c5a")
 
-    def step():
-        F.matmul(a, b, bias, flags=flags, out=y)
-        F.matmul_backward(dy, a, b, flags=flags, da=da, db=db, dbias=dbias, want_dbias=wl.bias)
+    def eager_step(pr=prob):
+        pr.forward()
+        pr.backward()
         if reduce_grads:
-            reduce_to_root(db.storage, dst=0)
-            if dbias is not None:
-                reduce_to_root(dbias.storage, dst=0)
+            for g in pr.weight_grads():
+                reduce_to_root(g, dst=0)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, after=None):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             fn()
+        if after:
+            after()
         e1.record()
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
@@ -218,105 +274,150 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    for _ in range(max(args.warmup, 3)):
-        step()
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        eager_step()
     F.device_status()
+
+    # Launch-bound workloads replay the step from a CUDA graph (same kernels, same order).
+    step, graphed = eager_step, False
+    est_ms = timed(eager_step, 5) / 5
+    if world == 1 and args.graph != "off" and (args.graph == "on" or est_ms < 0.2):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            eager_step()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            eager_step()
+        step, graphed = g.replay, True
+        for _ in range(3):
+            step()
+        F.device_status()
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-        time.sleep(0.25)
-    t_wall0 = time.time()
+        time.sleep(0.2)
     launches0 = F.launch_count()
+    eager_step()
+    launches_per_step = F.launch_count() - launches0
+    torch.cuda.synchronize()
+    t_wall0 = time.time()
     total_ms = timed(step, args.steps)
-    launches = F.launch_count() - launches0
     t_wall1 = time.time()
     F.device_status()
     ms_per_step = total_ms / args.steps
     value = wl.flops * world / (ms_per_step * 1e-3) / 1e12
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
 
-    # ---- roofline of the dominant kernel (the tensor-core GEMM; the skinny kernels for c5b) ----
-    m, k, n = wl.mkn
-    batch = int(np.prod(wl.out_shape[:-2])) if len(wl.out_shape) > 2 else 1
+    # ---- roofline of the dominant kernel: the forward launch(es) timed alone ----
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except OSError:
         pass
-
-    def fwd_only():
-        F.matmul(a, b, bias, flags=flags, out=y)
-    torch.cuda.synchronize()
     l0 = F.launch_count()
-    fwd_ms = timed(fwd_only, args.steps) / args.steps
-    fwd_launches = (F.launch_count() - l0) // args.steps
-    skinny = wl.name.startswith("c5b") or wl.name == "c3"
-    if skinny:
-        # HBM-bound shapes: each operand read once, the output written once.
-        alg_bytes = 4.0 * (np.prod(a.shape) + np.prod(b.shape) + np.prod(wl.out_shape))
+    prob.forward()
+    fwd_launches = F.launch_count() - l0
+    fwd_steps = min(args.steps, 50)
+    fwd_ms = timed(prob.forward, fwd_steps) / fwd_steps
+    if wl.name in HBM_BOUND:
+        if wl.kind == "attention":   # S written and read once, Q, K, V read, O written
+            alg_bytes = 4.0 * (2 * np.prod(wl.out_shape) + 4 * np.prod(wl.a_shape))
+        else:                        # each operand read once, the output written once
+            alg_bytes = 4.0 * (np.prod(wl.a_shape) + np.prod(wl.b_shape) + np.prod(wl.out_shape))
         peak = peaks.get("hbm_gbs", 6650.0)
         achieved = alg_bytes / (fwd_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": None, "kernel": "forward call", "launches_per_call": fwd_launches,
+                    "traffic": None, "kernel": "forward call(s): " + ("gemm_tc_kernel x2" if wl.kind == "attention"
+                                                                      else "skinny_fwd_kernel + reduce"),
+                    "launches_per_call": fwd_launches, "algorithmic_bytes": alg_bytes,
                     "peak_source": "measured hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650"}
     else:
-        alg = 2.0 * m * n * k * batch
         bf16 = peaks.get("bf16_tflops", 1590.0)
         peak = bf16 / 2.0
-        achieved = alg / (fwd_ms * 1e-3) / 1e12
+        achieved = wl.fwd_flops / (fwd_ms * 1e-3) / 1e12
         issued = achieved * (1 if args.precision == "tf32" else 3)
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "traffic": None, "kernel": "gemm_tc_kernel (forward GEMM launch, bias fused)",
                     "issued_tflops": issued, "issued_frac": issued / peak,
-                    "note": "3xTF32 issues 3 MMAs per product: algorithmic ceiling = peak/3" if args.precision != "tf32" else "single-pass TF32",
+                    "note": ("3xTF32 issues 3 MMAs per product: algorithmic ceiling = peak/3"
+                             if args.precision != "tf32" else "single-pass TF32"),
                     "peak_source": ("measured bf16_tflops/2 (no TF32 figure in MEASURED_PEAKS.json)"
                                     if "bf16_tflops" in peaks else "fallback 1590/2")}
 
     # ---- end to end: pinned host buffers -> device -> C ABI -> host buffers ------------------
-    def pin(x):
-        return torch.from_numpy(np.ascontiguousarray(x).reshape(-1)).pin_memory() if x is not None else None
-    h_in = [pin(x) for x in (a_np, b_np, bias_np, dy_np)]
-    d_in = [t.storage if t is not None else None for t in (a, b, bias, dy)]
-    outs = [t for t in (y, da, db, dbias) if t is not None]
-    h_out = [torch.empty(t.size, dtype=torch.float32).pin_memory() for t in outs]
-    h2d = sum(h.numel() * 4 for h in h_in if h is not None)
-    d2h = sum(h.numel() * 4 for h in h_out)
+    # Three streams: uploads, the C-ABI calls, downloads.  Inputs and outputs are double buffered on the
+    # device so that step i+1's upload and step i-1's download overlap step i's kernels; every step still
+    # moves all of its inputs in and all of its outputs out.
+    h_in = {k: torch.from_numpy(np.ascontiguousarray(v).reshape(-1)).pin_memory() for k, v in host.items()}
+    h_out = {k: torch.empty(t.size, dtype=torch.float32).pin_memory() for k, t in prob.out.items()}
+    h2d = sum(h.numel() * 4 for h in h_in.values())
+    d2h = sum(h.numel() * 4 for h in h_out.values())
+    s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+    slots = [prob, Problem(F, wl, host, dev, flags)]
+    ev_in = [torch.cuda.Event() for _ in slots]
+    ev_done = [torch.cuda.Event() for _ in slots]
+    ev_out = [torch.cuda.Event() for _ in slots]
+    counter = [0]
 
     def e2e_step():
-        for h, d in zip(h_in, d_in):
-            if h is not None:
-                d[: h.numel()].copy_(h, non_blocking=True)
-        step()
-        for h, t in zip(h_out, outs):
-            h.copy_(t.storage[: t.size], non_blocking=True)
+        i = counter[0] % len(slots)
+        counter[0] += 1
+        pr = slots[i]
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_done[i])          # the kernels that last read this slot's inputs are done
+            for key, h in h_in.items():
+                pr.inp[key].storage[: h.numel()].copy_(h, non_blocking=True)
+            ev_in[i].record(s_in)
+        s_main.wait_event(ev_in[i])
+        s_main.wait_event(ev_out[i])             # the download that last read this slot's outputs is done
+        eager_step(pr)
+        ev_done[i].record(s_main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_done[i])
+            for key, h in h_out.items():
+                t = pr.out[key]
+                h.copy_(t.storage[: t.size], non_blocking=True)
+            ev_out[i].record(s_out)
 
-    for _ in range(2):
+    def e2e_join():
+        s_main.wait_stream(s_in)
+        s_main.wait_stream(s_out)
+
+    for _ in range(3):
         e2e_step()
-    e2e_steps = max(3, min(args.steps, 10))
-    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    e2e_join()
+    torch.cuda.synchronize()
+    e2e_steps = max(4, min(args.steps, 50))
+    e2e_ms = timed(e2e_step, e2e_steps, after=e2e_join) / e2e_steps
     e2e_value = wl.flops * world / (e2e_ms * 1e-3) / 1e12
-    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    F.device_status()
 
     if rank == 0:
         cpu = cpu_baseline_sample(base, threads=1) if (world == 1 and not args.no_cpu) else None
+        ws = working_set_mb(wl)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None,
             "dtype": "f32 storage, 3xTF32 tensor-core arithmetic (f32 accumulate)" if args.precision != "tf32"
                      else "f32 storage, single-pass TF32 arithmetic (reduced precision mode)",
             "data": "synthetic (seeded numpy default_rng: x~U[0,1), W~N(0,0.02), b~N(0,0.02), dy~N(0,1))"
-                    if wl.name == "c2" else "synthetic (seeded numpy default_rng)",
+                    if wl.name == "c2" else "synthetic (seeded numpy default_rng, ~N(0,1))",
             "config": {"workload": f"{base.name}: {base.desc}", "per_gpu": f"{wl.a_shape} x {wl.b_logical}",
                        "parallelism": "single GPU" if world == 1 else
-                                      f"dp{world}: batch shard per rank, NCCL reduce of dW" + ("+db" if wl.bias else ""),
-                       "precision": args.precision,
-                       "l2": f"working set {working_set_mb(wl):.0f} MB per step vs 126 MB L2, no flush"
-                             if working_set_mb(wl) > 126 else "working set fits L2; buffers not flushed (stated)",
+                                      f"dp{world}: batch shard per rank" + (", NCCL reduce of dW" + ("+db" if wl.bias else "")
+                                                                            if reduce_grads else ", replicas"),
+                       "precision": args.precision, "cuda_graph": graphed,
+                       "l2": (f"working set {ws:.0f} MB per step vs 126 MB L2, no flush" if ws > 126 else
+                              f"working set {ws:.0f} MB fits the 126 MB L2; not flushed between steps (stated)"),
                        "flops_per_step_per_gpu": wl.flops},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms},
-            "gpu_launches": int(launches),
+                    "ms_per_step": e2e_ms, "overlap": "3 streams, 2 device slots"},
+            "gpu_launches": int(launches_per_step * args.steps),
             "clocks": clocks,
             "roofline": roofline,
         }
@@ -329,56 +430,60 @@ def run_ours(args):
 
 
 def working_set_mb(wl: Workload) -> float:
-    elems = 2 * np.prod(wl.a_shape) + 2 * np.prod(wl.b_shape) + 2 * np.prod(wl.out_shape)
+    if wl.kind == "attention":
+        elems = 2 * np.prod(wl.out_shape) + 8 * np.prod(wl.a_shape)
+    else:
+        elems = 2 * np.prod(wl.a_shape) + 2 * np.prod(wl.b_shape) + 2 * np.prod(wl.out_shape)
     return float(elems) * 4 / 1e6
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_step(O, wl: Workload, tensors, threads: int):
+def cpu_tensors(O, wl: Workload) -> dict:
+    host = wl.host_inputs(seed=0)
+    t = {k: O.HostTensor.from_array(v) for k, v in host.items()}
+    if wl.kind == "attention":
+        t["kt"] = O.permute(t["k"], wl.b_perm)
+    elif wl.b_perm:
+        t["b"] = O.permute(t["b"], wl.b_perm)
+    return t
+
+
+def cpu_step(O, wl: Workload, t: dict, threads: int):
     """The reference CPU backend's call sequence for one fwd+bwd step (oracle port)."""
-    a, b, bias, dy = tensors
-    y = O.matmul(a, b, threads=threads)                                    # ops/matmul.rs:19-78
-    if bias is not None:
-        y = O.add(y, bias)                                                 # ops/elementwise.rs:62-73
-        dy_in, _ = O.add_backward(dy, y.shape, bias.shape, threads=threads)  # :199-211
-    else:
-        dy_in = dy
-    return O.matmul_backward(dy_in, a, b, threads=threads)                 # ops/matmul.rs:200-222
+    if wl.kind == "attention":
+        s = O.matmul(t["q"], t["kt"], threads=threads)
+        O.matmul(s, t["v"], threads=threads)
+        ds, _ = O.matmul_backward(t["do"], s, t["v"], threads=threads)
+        return O.matmul_backward(ds, t["q"], t["kt"], threads=threads)
+    y = O.matmul(t["a"], t["b"], threads=threads)                              # ops/matmul.rs:19-78
+    dy = t["dy"]
+    if "bias" in t:
+        y = O.add(y, t["bias"])                                                # ops/elementwise.rs:62-73
+        dy, _ = O.add_backward(dy, y.shape, t["bias"].shape, threads=threads)  # :199-211
+    return O.matmul_backward(dy, t["a"], t["b"], threads=threads)              # ops/matmul.rs:200-222
 
 
-def cpu_tensors(O, wl: Workload):
-    a_np, b_np, bias_np, dy_np = wl.host_inputs(seed=0)
-    a, b = O.HostTensor.from_array(a_np), O.HostTensor.from_array(b_np)
-    if wl.b_perm:
-        b = O.permute(b, wl.b_perm)
-    bias = O.HostTensor.from_array(bias_np) if bias_np is not None else None
-    return a, b, bias, O.HostTensor.from_array(dy_np)
-
-
-def cpu_sample_workload(wl: Workload, budget_gflop: float) -> (Workload, str):
+def cpu_sample_workload(wl: Workload, budget_gflop: float):
     """Bounds the CPU work: whole step if it fits the budget, else a leading slice of the batch / rows."""
     if wl.flops / 1e9 <= budget_gflop:
         return wl, "whole step"
-    frac = budget_gflop * 1e9 / wl.flops
-    a_shape = list(wl.a_shape)
-    lead = a_shape[0]
-    keep = max(1, int(lead * frac))
-    a_shape[0] = keep
-    if len(wl.b_shape) == len(wl.a_shape) and wl.b_shape[0] == lead and len(wl.a_shape) > 2:
-        b_shape = list(wl.b_shape)
-        b_shape[0] = keep
-    else:
-        b_shape = wl.b_shape
-    small = Workload(wl.name, wl.desc, a_shape, b_shape, bias=wl.bias, b_perm=wl.b_perm, dist_a=wl.dist_a,
-                     dist_b=wl.dist_b, scale_b=wl.scale_b)
+    lead = wl.a_shape[0]
+    keep = max(1, int(lead * budget_gflop * 1e9 / wl.flops))
+    small = wl.with_a_shape((keep,) + tuple(wl.a_shape[1:]))
     return small, f"leading {keep}/{lead} of the first dim of A (same K, N)"
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 def cpu_baseline_sample(wl: Workload, threads: int) -> dict:
     import oracle as O
     O.build()
-    per_core = 6.0  # GFLOP/s order of magnitude of the scalar loop; only sizes the sample
-    small, what = cpu_sample_workload(wl, budget_gflop=20.0 * per_core * max(threads, 1))
+    small, what = cpu_sample_workload(wl, budget_gflop=120.0 * max(threads, 1))
     tens = cpu_tensors(O, small)
     t0 = time.perf_counter()
     cpu_step(O, small, tens, threads)
@@ -386,7 +491,7 @@ def cpu_baseline_sample(wl: Workload, threads: int) -> dict:
     return {"value": small.flops / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
             "sample": f"{what}; {small.flops / 1e9:.1f} GFLOP in {dt:.2f} s; C restatement of the reference's "
                       f"single-threaded CPU backend (gcc -O3 -ffp-contract=off)",
-            "host_cores": os.cpu_count()}
+            "host_cores": host_threads()}
 
 
 def run_reference(args):
@@ -396,7 +501,7 @@ def run_reference(args):
         return
     import oracle as O
     O.build()
-    threads = O.max_threads()
+    threads = host_threads()      # not OMP_NUM_THREADS: launchers set that to 1
     wl = WORKLOADS[args.workload]
     small, what = cpu_sample_workload(wl, budget_gflop=14.0 * threads)
     tens = cpu_tensors(O, small)
@@ -425,11 +530,13 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="replay the step from a CUDA graph (auto: only for steps under 0.2 ms)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
