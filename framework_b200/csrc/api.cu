@@ -291,7 +291,7 @@ int fwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, float *out
     if (s.K == 0) return zero_or_bias_fill(c, out, s.batch * s.M, s.N, bias, accumulate);
 
     const bool want_skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
-                             ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 16);
+                             ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 8);
     if (want_skinny && s.batch == 1 && skinny_fwd_supported(s.M, s.N, s.K)) {
         const int an = a->ndim, bn = b->ndim;
         const bool a_ok = a->stride[an - 1] == 1 || s.K == 1;
@@ -449,7 +449,7 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
             if (rc) return rc;
         } else {
             const bool want_skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
-                                     ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 16);
+                                     ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 8);
             const bool plain2d = s.batch == 1 && g_batch == 1 && s.M <= 16;
             if (want_skinny && plain2d && (a->stride[a->ndim - 1] == 1 || s.K == 1) &&
                 (dc->stride[gn - 1] == 1 || s.N == 1)) {

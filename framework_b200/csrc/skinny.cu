@@ -3,7 +3,7 @@
 // HBM, not by the tensor pipe; they run as CUDA-core fp32 FMA kernels with 16-byte
 // loads and a split of the contraction over the grid.
 //
-//   fwd : y[M,N]  = x[M,K] . W[K,N] (+bias)        W streamed once, split-K partials
+//   fwd : y[M,N]  = x[M,K] . W[K,N] (+bias)        W streamed once, split-K partials, fused finish
 //   dW  : dW[K,N] = x[M,K]^T . dy[M,N]             dW written once
 // (dx = dy . W^T is a K-major/K-major product and goes through the tensor-core kernel.)
 #include "internal.h"
@@ -16,84 +16,169 @@ namespace {
 
 constexpr int kSkinnyThreads = 128;   // each thread owns 4 consecutive output columns
 
-// grid = (n strips of 512 columns, k splits).  x[M, k-slice] is staged in shared memory.
+// Tickets of the fused split-K finish: one counter per 512-column strip.  The block that takes the
+// last ticket of a strip sums that strip's partials; it puts the counter back to zero, so the array
+// is clean again when the kernel ends.
+constexpr int kMaxStrips = 1024;
+constexpr int kFwdGroups = 4;                              // k-groups per block
+constexpr int kFwdThreads = kSkinnyThreads * kFwdGroups;   // 512
+__device__ unsigned int g_skinny_tickets[kMaxStrips];
+
+// grid = (n strips of 512 columns, k splits), 512 threads = 128 column-threads x 4 k-groups.
+// x[M, k-slice] is staged in shared memory; each k-group streams its quarter of the block's W rows
+// with 16-byte loads, a batch of U rows in flight per thread while the previous batch is multiplied.
+// The four groups are added through shared memory in group order, the block's sum goes to scratch,
+// and the last block to finish a strip adds the strip's partials in ascending split order, applies
+// bias / accumulate and writes y.  Every sum has a fixed order: results do not depend on scheduling.
 template <int MT>
-__global__ void __launch_bounds__(kSkinnyThreads)
+__global__ void __launch_bounds__(kFwdThreads)
 skinny_fwd_kernel(const float *__restrict__ x, long long ldx, const float *__restrict__ W, long long ldw,
-                  float *__restrict__ partial, int M, long long N, long long K, long long k_per) {
-    extern __shared__ float xs[];   // [MT][k_per]
+                  float *__restrict__ partial, float *__restrict__ y, long long ldy,
+                  const float *__restrict__ bias, int accumulate, int M, long long N, long long K,
+                  long long k_per) {
+    constexpr int U = MT <= 2 ? 8 : 4;
+    extern __shared__ float smem_f[];
+    float *xs = smem_f;                                                  // [MT][k_per]
+    float4 *red = reinterpret_cast<float4 *>(smem_f + MT * k_per);       // [groups-1][MT][128]
+    __shared__ unsigned int s_ticket;
+    const int kg = threadIdx.x / kSkinnyThreads, ct = threadIdx.x % kSkinnyThreads;
     const long long k0 = blockIdx.y * k_per;
     const long long k1 = min(K, k0 + k_per);
     const int kc = static_cast<int>(k1 - k0);
-    for (int i = threadIdx.x; i < MT * static_cast<int>(k_per); i += kSkinnyThreads) {
+    const int g0 = (kc * kg / kFwdGroups) & ~3;
+    const int g1 = kg == kFwdGroups - 1 ? kc : ((kc * (kg + 1) / kFwdGroups) & ~3);
+    const long long col = (static_cast<long long>(blockIdx.x) * kSkinnyThreads + ct) * 4;
+    const bool live = col < N;
+    const bool vec = col + 3 < N;
+    const float *wp = W + k0 * ldw + col;
+    float4 w[U];
+    if (vec && g0 + U <= g1) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) w[u] = __ldcs(reinterpret_cast<const float4 *>(wp + (g0 + u) * ldw));
+    }
+    for (int i = threadIdx.x; i < MT * static_cast<int>(k_per); i += kFwdThreads) {
         const int m = i / static_cast<int>(k_per), kk = i - m * static_cast<int>(k_per);
         xs[i] = (m < M && kk < kc) ? __ldg(x + m * ldx + k0 + kk) : 0.f;
     }
     __syncthreads();
-    const long long col = (static_cast<long long>(blockIdx.x) * kSkinnyThreads + threadIdx.x) * 4;
-    if (col >= N) return;
-    const bool vec = col + 3 < N;
     float4 acc[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m] = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float *wp = W + k0 * ldw + col;
-    int kk = 0;
+    int kk = g0;
     if (vec) {
-        for (; kk + 4 <= kc; kk += 4) {
-            float4 w[4];
+        for (; kk + U <= g1; kk += U) {
+            float4 wn[U];
+            const bool more = kk + 2 * U <= g1;
+            if (more) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) w[u] = __ldcs(reinterpret_cast<const float4 *>(wp + (kk + u) * ldw));
+                for (int u = 0; u < U; ++u) wn[u] = __ldcs(reinterpret_cast<const float4 *>(wp + (kk + U + u) * ldw));
+            }
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-                const float4 xv = *reinterpret_cast<const float4 *>(xs + m * k_per + kk);
-                const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    acc[m].x = fmaf(xa[u], w[u].x, acc[m].x);
-                    acc[m].y = fmaf(xa[u], w[u].y, acc[m].y);
-                    acc[m].z = fmaf(xa[u], w[u].z, acc[m].z);
-                    acc[m].w = fmaf(xa[u], w[u].w, acc[m].w);
+                for (int u4 = 0; u4 < U; u4 += 4) {
+                    const float4 xv = *reinterpret_cast<const float4 *>(xs + m * k_per + kk + u4);
+                    const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        acc[m].x = fmaf(xa[u], w[u4 + u].x, acc[m].x);
+                        acc[m].y = fmaf(xa[u], w[u4 + u].y, acc[m].y);
+                        acc[m].z = fmaf(xa[u], w[u4 + u].z, acc[m].z);
+                        acc[m].w = fmaf(xa[u], w[u4 + u].w, acc[m].w);
+                    }
                 }
+            }
+            if (more) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) w[u] = wn[u];
             }
         }
     }
-    for (; kk < kc; ++kk) {
-        float w[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int e = 0; e < 4; ++e)
-            if (col + e < N) w[e] = __ldg(wp + kk * ldw + e);
+    if (live) {
+        for (; kk < g1; ++kk) {
+            float wr[4] = {0.f, 0.f, 0.f, 0.f};
+            if (vec) {
+                const float4 t = __ldcs(reinterpret_cast<const float4 *>(wp + kk * ldw));
+                wr[0] = t.x; wr[1] = t.y; wr[2] = t.z; wr[3] = t.w;
+            } else {
+                for (int e = 0; e < 4; ++e)
+                    if (col + e < N) wr[e] = __ldg(wp + kk * ldw + e);
+            }
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            const float xv = xs[m * k_per + kk];
-            acc[m].x = fmaf(xv, w[0], acc[m].x);
-            acc[m].y = fmaf(xv, w[1], acc[m].y);
-            acc[m].z = fmaf(xv, w[2], acc[m].z);
-            acc[m].w = fmaf(xv, w[3], acc[m].w);
+            for (int m = 0; m < MT; ++m) {
+                const float xv = xs[m * k_per + kk];
+                acc[m].x = fmaf(xv, wr[0], acc[m].x);
+                acc[m].y = fmaf(xv, wr[1], acc[m].y);
+                acc[m].z = fmaf(xv, wr[2], acc[m].z);
+                acc[m].w = fmaf(xv, wr[3], acc[m].w);
+            }
         }
     }
-    float *out = partial + static_cast<long long>(blockIdx.y) * M * N;
+    // k-groups 1..3 hand their sums to group 0 through shared memory.
+    if (kg > 0) {
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        if (m >= M) break;
-        float *o = out + m * N + col;
-        const float a[4] = {acc[m].x, acc[m].y, acc[m].z, acc[m].w};
-        for (int e = 0; e < 4; ++e)
-            if (col + e < N) o[e] = a[e];
+        for (int m = 0; m < MT; ++m) red[((kg - 1) * MT + m) * kSkinnyThreads + ct] = acc[m];
     }
-}
-
-// y[m, j] = sum over splits (ascending) (+ bias[j]) (+ y[m, j])
-__global__ void skinny_reduce_kernel(const float *__restrict__ partial, float *__restrict__ y, long long ldy,
-                                     const float *__restrict__ bias, int accumulate, int splits, int M,
-                                     long long N) {
-    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-    if (i >= M * N) return;
-    const long long j = i % N;
-    const int m = static_cast<int>(i / N);
-    float s = partial[i];
-    for (int sp = 1; sp < splits; ++sp) s += partial[static_cast<long long>(sp) * M * N + i];
-    if (bias) s += __ldg(bias + j);
-    float *dst = y + m * ldy + j;
-    *dst = accumulate ? *dst + s : s;
+    __syncthreads();
+    if (kg == 0 && live) {
+        float *out = partial + static_cast<long long>(blockIdx.y) * M * N;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m >= M) break;
+            float4 a = acc[m];
+#pragma unroll
+            for (int g = 0; g < kFwdGroups - 1; ++g) {
+                const float4 t = red[(g * MT + m) * kSkinnyThreads + ct];
+                a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+            }
+            float *o = out + m * N + col;
+            const float av[4] = {a.x, a.y, a.z, a.w};
+            for (int e = 0; e < 4; ++e)
+                if (col + e < N) __stcg(o + e, av[e]);
+        }
+    }
+    // Fused finish: the block holding the strip's last ticket reduces it; k-group g takes rows g, g+4, ...
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_ticket = atomicAdd(&g_skinny_tickets[blockIdx.x], 1u);
+    __syncthreads();
+    if (s_ticket != gridDim.y - 1) return;
+    __threadfence();
+    if (live) {
+        const int splits = static_cast<int>(gridDim.y);
+        const long long slab = static_cast<long long>(M) * N;
+        const bool vec4 = vec && (N & 3) == 0;
+        for (int m = kg; m < M; m += kFwdGroups) {
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            const float *src = partial + m * N + col;
+            if (vec4) {
+                int sp = 0;
+                for (; sp + 8 <= splits; sp += 8) {      // 8 independent loads in flight, added in order
+                    float4 t[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) t[u] = __ldcg(reinterpret_cast<const float4 *>(src + (sp + u) * slab));
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) { sum[0] += t[u].x; sum[1] += t[u].y; sum[2] += t[u].z; sum[3] += t[u].w; }
+                }
+                for (; sp < splits; ++sp) {
+                    const float4 t = __ldcg(reinterpret_cast<const float4 *>(src + sp * slab));
+                    sum[0] += t.x; sum[1] += t.y; sum[2] += t.z; sum[3] += t.w;
+                }
+            } else {
+                for (int sp = 0; sp < splits; ++sp)
+                    for (int e = 0; e < 4; ++e)
+                        if (col + e < N) sum[e] += __ldcg(src + sp * slab + e);
+            }
+            for (int e = 0; e < 4; ++e) {
+                if (col + e >= N) break;
+                float v = sum[e];
+                if (bias) v += __ldg(bias + col + e);
+                float *dst = y + m * ldy + col + e;
+                *dst = accumulate ? *dst + v : v;
+            }
+        }
+    }
+    if (threadIdx.x == 0) g_skinny_tickets[blockIdx.x] = 0u;
 }
 
 // grid = (n strips of 512 columns, k slabs).  dy[M, 4 cols] lives in registers; each
@@ -149,12 +234,12 @@ struct FwdPlan { int splits; long long k_per; int strips; };
 FwdPlan fwd_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
     FwdPlan pl;
     pl.strips = static_cast<int>((N + 4 * kSkinnyThreads - 1) / (4 * kSkinnyThreads));
-    // Enough blocks to fill the GPU a few times over, but keep the partial traffic
-    // (splits * M * N * 8 bytes) well under the weight traffic (K * N * 4 bytes).
-    long long want = std::max<long long>(1, (sm_count * 4LL) / pl.strips);
+    // Two 512-thread blocks per SM in total, but keep the partial traffic (splits * M * N * 8 bytes)
+    // well under the weight traffic (K * N * 4 bytes) and every k-group at least 8 rows deep.
+    long long want = std::max<long long>(1, (sm_count * 2LL) / pl.strips);
     long long cap = std::max<long long>(1, K / (16 * std::max<int64_t>(M, 1)));
     long long splits = std::min(want, cap);
-    splits = std::min<long long>(splits, (K + 15) / 16);
+    splits = std::min<long long>(splits, std::max<long long>(1, K / (8 * kFwdGroups)));
     splits = std::max<long long>(splits, (K + 2047) / 2048);   // shared-memory bound on a k slice
     pl.k_per = ((K + splits - 1) / splits + 3) & ~3LL;
     pl.splits = static_cast<int>((K + pl.k_per - 1) / pl.k_per);
@@ -178,24 +263,22 @@ int launch_skinny_fwd(const float *x, int64_t ldx, const float *W, int64_t ldw, 
     const FwdPlan pl = fwd_plan(M, N, K, sm_count);
     const int mt = pick_mt(M);
     dim3 grid(pl.strips, pl.splits);
-    const size_t smem = static_cast<size_t>(mt) * pl.k_per * sizeof(float);
+    const size_t smem = static_cast<size_t>(mt) * pl.k_per * sizeof(float) +
+                        static_cast<size_t>(kFwdGroups - 1) * mt * kSkinnyThreads * sizeof(float4);
     const bool vec_w = (ldw % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
     if (!vec_w) return fail(MNI_B200_ERR_ARG, "skinny path needs a 16-byte aligned weight with ld %% 4 == 0");
+    if (pl.strips > kMaxStrips) return fail(MNI_B200_ERR_ARG, "skinny path: N too large");
 #define MNI_SKINNY_FWD(MT)                                                                             \
     case MT:                                                                                           \
         cudaFuncSetAttribute(skinny_fwd_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
-        skinny_fwd_kernel<MT><<<grid, kSkinnyThreads, smem, stream>>>(x, ldx, W, ldw, partial, (int)M, N, K, \
-                                                                      pl.k_per);                       \
+        skinny_fwd_kernel<MT><<<grid, kFwdThreads, smem, stream>>>(x, ldx, W, ldw, partial, y, ldy, bias,    \
+                                                                      accumulate ? 1 : 0, (int)M, N, K, pl.k_per); \
         break;
     switch (mt) {
         MNI_SKINNY_FWD(1) MNI_SKINNY_FWD(2) MNI_SKINNY_FWD(4) MNI_SKINNY_FWD(8) MNI_SKINNY_FWD(16)
     }
 #undef MNI_SKINNY_FWD
     MNI_LAUNCH_CHECK("skinny_fwd_kernel");
-    const long long total = M * N;
-    skinny_reduce_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
-        partial, y, ldy, bias, accumulate ? 1 : 0, pl.splits, static_cast<int>(M), N);
-    MNI_LAUNCH_CHECK("skinny_reduce_kernel");
     return MNI_B200_OK;
 }
 
