@@ -176,6 +176,43 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
 }
+// ---- CTA-pair (cta_group::2) forms: one MMA spans two SMs; the leader CTA issues it.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in CTA `cta` of the cluster.
+__device__ __forceinline__ void mbar_arrive_cta(uint32_t bar, uint32_t cta) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(bar), "r"(cta)
+        : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Commit that arrives on the barrier at this offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(static_cast<uint16_t>(3))
+        : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -257,12 +294,17 @@ __device__ __forceinline__ void load_operand(int mode, uint32_t dst, const CUten
     }
 }
 
-template <int BN, int BK, bool FAST, int NS>
+// CG = 1: one CTA computes a 128 x BN tile.  CG = 2: a pair of CTAs (a 2-CTA cluster) computes a
+// 256 x BN tile with cta_group::2 MMAs issued by the pair's leader; each CTA stages its own 128 rows
+// of A and half (BN/2 rows) of B, so shared-memory and L2 traffic per flop drop by a third.
+template <int BN, int BK, bool FAST, int NS, int CG>
 __global__ void __launch_bounds__(32 * (6 + NS), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const KParams p) {
+    static_assert(CG == 1 || (CG == 2 && !FAST), "CTA pairs are built for the 3xTF32 mode only");
+    constexpr int BNL = BN / CG;                           // B rows staged by this CTA
     constexpr uint32_t A_BYTES = BM * BK * 4;
-    constexpr uint32_t B_BYTES = BN * BK * 4;
+    constexpr uint32_t B_BYTES = BNL * BK * 4;
     constexpr uint32_t RAW_BYTES = A_BYTES + B_BYTES;
     constexpr uint32_t STAGE_BYTES = FAST ? RAW_BYTES : 2 * RAW_BYTES;
     constexpr uint32_t STAGE16 = STAGE_BYTES >> 4;
@@ -288,30 +330,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const long long t_kernel0 = clock64();
+    const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;   // 0 = the pair's leader
+    const int unit0 = static_cast<int>(blockIdx.x) / CG;           // this CTA (pair) starts at this unit ...
+    const int unit_step = static_cast<int>(gridDim.x) / CG;        // ... and strides by the number of CTAs (pairs)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(bar_full + 8u * s, 1);
-            mbar_init(bar_xform + 8u * s, 32 * NS);
+            mbar_init(bar_xform + 8u * s, CG * 32 * NS);   // split threads of both CTAs arrive on the leader's
             mbar_init(bar_empty + 8u * s, 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_acc_full + 8u * i, 1);
-            mbar_init(bar_acc_empty + 8u * i, 128);
+            mbar_init(bar_acc_empty + 8u * i, CG * 128);   // epilogue threads of both CTAs arrive on the leader's
         }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                         smem_u32(tmem_slot)),
-                     "r"(TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (CG == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(tmem_slot)),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(tmem_slot)),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (CG == 2) cluster_sync_all();   // the peer's barriers exist before anyone arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -329,7 +383,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             constexpr uint32_t CHUNK_BYTES = 128u * BK;   // one 32-wide MN chunk: BK k-rows of 128 bytes
             const uint32_t dstA0 = smem_u32(stage_base);
             uint32_t dstA = dstA0;
-            for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
+            for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
                 const TileCoord t = decode_unit(p, unit);
                 int f = 0, kk = t.it0;
                 if (p.fold > 1 || p.splits > 1) {
@@ -339,7 +393,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 int a0, a1, a2, b0, b1, b2;
                 batch_coords(t.bt * p.fold + f, p.a_batch, p.a_d1, p.a_d2, a0, a1, a2);
                 batch_coords(t.bt * p.fold + f, p.b_batch, p.b_d1, p.b_d2, b0, b1, b2);
-                const int rowA = t.tm * BM, rowB = t.tn * BN;
+                const int rowA = t.tm * (BM * CG) + static_cast<int>(cta_rank) * BM;
+                const int rowB = t.tn * BN + static_cast<int>(cta_rank) * BNL;
                 for (int it = t.it0; it < t.it1; ++it) {
                     ok = mbar_wait_warp(bar_empty + 8u * stage, phase ^ 1u, abort_flag, p.err, 0x100u | stage, waited);
                     if (!ok) break;
@@ -348,7 +403,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (elect_one()) {
                         mbar_arrive_expect_tx(full, RAW_BYTES);
                         load_operand(p.a_mode, dstA, &tmA, full, k0, rowA, BM / 32, CHUNK_BYTES, a0, a1, a2);
-                        load_operand(p.b_mode, dstA + A_BYTES, &tmB, full, k0, rowB, BN / 32, CHUNK_BYTES, b0, b1, b2);
+                        load_operand(p.b_mode, dstA + A_BYTES, &tmB, full, k0, rowB, BNL / 32, CHUNK_BYTES, b0, b1, b2);
                     }
                     ++armed;
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; dstA = dstA0; } else { dstA += STAGE_BYTES; }
@@ -375,8 +430,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        // The whole warp runs the loop; one elected lane issues each MMA and commit.
-        {
+        // The whole warp runs the loop; one elected lane issues each MMA and commit.  In a CTA pair
+        // only the leader's warp issues (its MMAs drive both SMs); the peer's warp just holds TMEM.
+        if (CG == 1 || cta_rank == 0) {
             int stage = 0;
             uint32_t phase = 0;
             int acc_it = 0;
@@ -390,7 +446,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t a_ks = p.a_kstep, b_ks = p.b_kstep;
             const uint32_t idesc = p.idesc;
             const uint32_t ready0 = FAST ? bar_full : bar_xform;
-            for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
+            for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
                 const int iters = unit_iters(p, unit);
                 const int buf = acc_it & 1;
                 const uint32_t acc_phase = (acc_it >> 1) & 1;
@@ -406,7 +462,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                     for (int ks = 0; ks < KSTEPS; ++ks) {
                         const uint32_t ak = a_lo + ks * a_ks, bk = b_lo + ks * b_ks;
-                        if (FAST) {
+                        if constexpr (CG == 2) {
+                            if (elect_one()) umma_tf32_pair(d_tmem, ak + LO16, a_hi, bk, b_hi, idesc, accumulate);
+                            if (elect_one()) umma_tf32_pair(d_tmem, ak, a_hi, bk + LO16, b_hi, idesc, 1u);
+                            if (elect_one()) umma_tf32_pair(d_tmem, ak, a_hi, bk, b_hi, idesc, 1u);
+                        } else if (FAST) {
                             if (elect_one()) umma_tf32(d_tmem, ak, a_hi, bk, b_hi, idesc, accumulate);
                         } else {
                             if (elect_one()) umma_tf32(d_tmem, ak + LO16, a_hi, bk, b_hi, idesc, accumulate);
@@ -415,7 +475,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                         accumulate = 1u;
                     }
-                    if (elect_one()) umma_commit(bar_empty + 8u * stage);
+                    if constexpr (CG == 2) { if (elect_one()) umma_commit_pair(bar_empty + 8u * stage); }
+                    else { if (elect_one()) umma_commit(bar_empty + 8u * stage); }
                     if (++stage == p.stages) {
                         stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0;
                     } else {
@@ -423,7 +484,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                 }
                 if (!ok) break;
-                if (elect_one()) umma_commit(bar_acc_full + 8u * buf);
+                if constexpr (CG == 2) { if (elect_one()) umma_commit_pair(bar_acc_full + 8u * buf); }
+                else { if (elect_one()) umma_commit(bar_acc_full + 8u * buf); }
                 ++acc_it;
             }
             if (p.prof && lane == 0) {
@@ -444,7 +506,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             constexpr int PER = N4 / NT;                  // float4s per thread
             constexpr int U = (PER % 4 == 0) ? 4 : (PER % 2 == 0 ? 2 : 1);
             static_assert(N4 % NT == 0 && PER % U == 0, "stage size must divide over the split warps");
-            for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
+            for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
                 const int iters = unit_iters(p, unit);
                 for (int it = 0; it < iters; ++it) {
                     ok = mbar_wait(bar_full + 8u * stage, phase, abort_flag, p.err, 0x400u | stage, waited);
@@ -467,7 +529,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    mbar_arrive(bar_xform + 8u * stage);
+                    if (CG == 2 && cta_rank != 0) mbar_arrive_cta(bar_xform + 8u * stage, 0u);
+                    else mbar_arrive(bar_xform + 8u * stage);
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -484,7 +547,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         long long waited = 0;
         const bool use_tma = p.epi_mode != kEpiPlainStores;
         const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
-        for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
+        for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
             const TileCoord t = decode_unit(p, unit);
             const int buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
@@ -493,7 +556,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (!ok) break;
             tc_fence_after();
             const bool fuse = p.splits == 1;
-            const int row0 = t.tm * BM + q * 32;
+            const int row0 = t.tm * (BM * CG) + static_cast<int>(cta_rank) * BM + q * 32;
             const int cbatch = fuse ? t.bt : t.split * p.batch + t.bt;
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
             if (row0 < p.M) {
@@ -560,7 +623,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
             }
             tc_fence_before();
-            mbar_arrive(bar_acc_empty + 8u * buf);
+            if (CG == 2 && cta_rank != 0) mbar_arrive_cta(bar_acc_empty + 8u * buf, 0u);
+            else mbar_arrive(bar_acc_empty + 8u * buf);
             ++acc_it;
         }
         if (use_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -573,11 +637,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         atomicAdd(p.prof + 5, static_cast<unsigned long long>(clock64() - t_kernel0));
         atomicAdd(p.prof + 6, 1ull);
     }
+    if constexpr (CG == 2) cluster_sync_all();   // both CTAs are done with the pair's TMEM and barriers
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
-                     : "memory");
+        if constexpr (CG == 2)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                         : "memory");
     }
 }
 
@@ -721,7 +790,7 @@ int make_output_map(CUtensorMap *map, float *ptr, int64_t N, int64_t M, int64_t 
 }
 
 struct Plan {
-    int bn, bk, stages, splits, tiles_m, tiles_n, grid;
+    int bn, bk, cg, stages, splits, tiles_m, tiles_n, grid;   // cg = CTAs per tile (1, or 2 = CTA pair)
     size_t smem;
 };
 
@@ -732,31 +801,35 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     pl.bn = p.N <= 64 ? 64 : (p.N <= 128 ? 128 : 256);
     const int bn_env = env_int("MNI_B200_BN", 0);
     if (bn_env == 64 || bn_env == 128 || bn_env == 256) pl.bn = bn_env;
+    // CTA pairs: 3xTF32 mode, 256-wide tiles, and at least two 128-row blocks of output.
+    pl.cg = (!p.fast_tf32 && pl.bn == 256 && p.M > BM && env_int("MNI_B200_CTA_PAIR", 1) != 0) ? 2 : 1;
     pl.bk = (pl.bn == 256 && !p.fast_tf32) ? 16 : 32;
     const int bk_env = env_int("MNI_B200_BK", 0);
     if (bk_env == 16 || bk_env == 32) pl.bk = bk_env;
-    const size_t raw = static_cast<size_t>(BM + pl.bn) * pl.bk * 4;
+    const size_t raw = static_cast<size_t>(BM + pl.bn / pl.cg) * pl.bk * 4;
     const size_t stage = p.fast_tf32 ? raw : 2 * raw;
     const size_t budget = 227 * 1024;
     pl.stages = static_cast<int>(std::min<size_t>(kMaxStages, (budget - kFixedSmem) / stage));
     const int st_env = env_int("MNI_B200_STAGES", 0);
     if (st_env >= 1 && st_env <= pl.stages) pl.stages = st_env;
     pl.smem = kFixedSmem + static_cast<size_t>(pl.stages) * stage;
-    pl.tiles_m = static_cast<int>((p.M + BM - 1) / BM);
+    const int tile_m = BM * pl.cg;
+    const int slots = std::max(1, sm_count / pl.cg);          // CTAs (or CTA pairs) that run at once
+    pl.tiles_m = static_cast<int>((p.M + tile_m - 1) / tile_m);
     pl.tiles_n = static_cast<int>((p.N + pl.bn - 1) / pl.bn);
     const long long tiles = static_cast<long long>(p.batch) * pl.tiles_m * pl.tiles_n;
     const long long iters = p.fold * ((p.K + pl.bk - 1) / pl.bk);
     int splits = 1;
     if (p.force_splits > 0) {
         splits = p.force_splits;
-    } else if (tiles * 2 <= sm_count && iters >= 8) {
+    } else if (tiles * 2 <= slots && iters >= 8) {
         // Few output tiles and a long contraction: split K so that the whole GPU works.
-        splits = static_cast<int>(std::min<long long>(sm_count / tiles, iters / 4));
+        splits = static_cast<int>(std::min<long long>(slots / tiles, iters / 4));
     }
     splits = static_cast<int>(std::max<long long>(1, std::min<long long>(std::min<long long>(splits, iters), 64)));
     pl.splits = splits;
     const long long units = tiles * splits;
-    pl.grid = static_cast<int>(std::min<long long>(units, sm_count));
+    pl.grid = static_cast<int>(std::min<long long>(units, slots)) * pl.cg;
     return pl;
 }
 
@@ -765,17 +838,29 @@ uint32_t desc_hi_bits(uint32_t sbo_bytes, uint32_t layout_type) {
     return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (layout_type << 29);
 }
 
-template <int BN, int BK, bool FAST, int NS>
+template <int BN, int BK, bool FAST, int NS, int CG>
 cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
                            const KParams &k, cudaStream_t stream) {
     static std::once_flag once;
     static cudaError_t attr = cudaSuccess;
     std::call_once(once, [] {
-        attr = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FAST, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        attr = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FAST, NS, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    227 * 1024);
     });
     if (attr != cudaSuccess) return attr;
-    gemm_tc_kernel<BN, BK, FAST, NS><<<pl.grid, 32 * (6 + NS), pl.smem, stream>>>(tmA, tmB, tmC, k);
-    return cudaSuccess;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(pl.grid));
+    cfg.blockDim = dim3(32 * (6 + NS));
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = CG;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = CG == 2 ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK, FAST, NS, CG>, tmA, tmB, tmC, k);
 }
 
 }  // namespace
@@ -824,7 +909,7 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     CUtensorMap tmA, tmB, tmC;
     int rc = make_operand_map(&tmA, p.A, BM, pl.bk, &k.a_mode);
     if (rc) return rc;
-    rc = make_operand_map(&tmB, p.B, pl.bn, pl.bk, &k.b_mode);
+    rc = make_operand_map(&tmB, p.B, pl.bn / pl.cg, pl.bk, &k.b_mode);
     if (rc) return rc;
 
     // Epilogue: TMA store when the destination rows are 16-byte aligned, plain stores otherwise.
@@ -861,7 +946,7 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     k.stages = pl.stages;
     k.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.A.k_major ? 0u : 1u) << 15) |
               ((p.B.k_major ? 0u : 1u) << 16) | (static_cast<uint32_t>(pl.bn >> 3) << 17) |
-              (static_cast<uint32_t>(BM >> 4) << 24);
+              (static_cast<uint32_t>((BM * pl.cg) >> 4) << 24);
     // K-major tile: rows of BK floats, 8-row groups SBO apart, swizzle span = one row.
     // MN-major tile: 32-float chunks of BK k-rows (LBO apart); the 32-byte-unit swizzle repeats every
     // 4 k-rows (SBO = 512), and one 8-deep k-step spans two such groups (1024 bytes).
@@ -885,11 +970,13 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     cudaError_t e = cudaErrorInvalidValue;
     const int split_warps = env_int("MNI_B200_SPLIT_WARPS", 8);
 #define MNI_VARIANT(BN_, BK_)                                                                         \
-    if (pl.bn == BN_ && pl.bk == BK_) {                                                               \
-        if (p.fast_tf32) e = launch_variant<BN_, BK_, true, 4>(pl, tmA, tmB, tmC, k, stream);         \
-        else if (split_warps == 8) e = launch_variant<BN_, BK_, false, 8>(pl, tmA, tmB, tmC, k, stream); \
-        else e = launch_variant<BN_, BK_, false, 4>(pl, tmA, tmB, tmC, k, stream);                    \
+    if (pl.cg == 1 && pl.bn == BN_ && pl.bk == BK_) {                                                 \
+        if (p.fast_tf32) e = launch_variant<BN_, BK_, true, 4, 1>(pl, tmA, tmB, tmC, k, stream);      \
+        else if (split_warps == 8) e = launch_variant<BN_, BK_, false, 8, 1>(pl, tmA, tmB, tmC, k, stream); \
+        else e = launch_variant<BN_, BK_, false, 4, 1>(pl, tmA, tmB, tmC, k, stream);                 \
     }
+    if (pl.cg == 2 && pl.bk == 16) e = launch_variant<256, 16, false, 8, 2>(pl, tmA, tmB, tmC, k, stream);
+    if (pl.cg == 2 && pl.bk == 32) e = launch_variant<256, 32, false, 8, 2>(pl, tmA, tmB, tmC, k, stream);
     MNI_VARIANT(64, 16) MNI_VARIANT(64, 32) MNI_VARIANT(128, 16) MNI_VARIANT(128, 32) MNI_VARIANT(256, 16)
     MNI_VARIANT(256, 32)
 #undef MNI_VARIANT
