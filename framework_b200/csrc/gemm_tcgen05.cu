@@ -40,12 +40,11 @@ namespace {
 constexpr int BM = 128;
 constexpr int kMaxStages = 8;
 constexpr int kEpiBufBytes = 32 * 128;                     // one 32 x 32 f32 patch
-constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;            // 4 epilogue warps, double buffered
 constexpr int kBarBytes = (3 * kMaxStages + 4) * 8 + 16;
 constexpr long long kWaitCycles = 4000000000LL;            // ~2 s at 2 GHz
 
 enum OperandMode { kKMajor = 0, kMnMultiBox = 1, kMnSingleBox = 2 };
-enum EpilogueMode { kEpiPlainStores = 0, kEpiTmaStore = 1, kEpiTmaReduce = 2 };
+enum EpilogueMode { kEpiPlainStores = 0, kEpiTmaStore = 1, kEpiTmaReduce = 2, kEpiVectorStores = 3 };
 
 struct KParams {
     int M, N;
@@ -59,6 +58,7 @@ struct KParams {
     int a_mode, b_mode;        // OperandMode
     int stages;
     int epi_mode;              // EpilogueMode
+    int epi_patches;           // staging patches per epilogue warp: TMA stores in flight per warp
     uint32_t idesc;
     uint32_t a_desc_hi, b_desc_hi;   // upper 32 bits of the smem descriptors (SBO | version | layout)
     uint32_t a_desc_lbo, b_desc_lbo; // LBO field, already shifted into the low word
@@ -317,7 +317,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                                 ~static_cast<uintptr_t>(1023));
     uint8_t *stage_base = smem;
     uint8_t *epi_base = smem + static_cast<size_t>(p.stages) * STAGE_BYTES;      // 1024-aligned
-    uint64_t *bars = reinterpret_cast<uint64_t *>(epi_base + kEpiBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(epi_base + 4 * p.epi_patches * kEpiBufBytes);
     // bars: full[S] | xform[S] | empty[S] | acc_full[2] | acc_empty[2]
     const uint32_t bar_full = smem_u32(bars);
     const uint32_t bar_xform = bar_full + 8u * kMaxStages;
@@ -539,13 +539,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else {
         // ------------------------------------------------------------ epilogue
         const int q = warp & 3;                       // TMEM lane quarter this warp may read
-        uint8_t *my_stage = epi_base + (warp - (2 + NS)) * 2 * kEpiBufBytes;
+        uint8_t *my_stage = epi_base + (warp - (2 + NS)) * p.epi_patches * kEpiBufBytes;
         int acc_it = 0;
         int patch = 0;                                // staging buffer to use next
         int in_flight = 0;                            // bulk groups committed by lane 0 and not yet waited for
         bool ok = true;
-        long long waited = 0;
-        const bool use_tma = p.epi_mode != kEpiPlainStores;
+        long long waited = 0, t_ld = 0, t_wg = 0;
+        const bool use_tma = p.epi_mode == kEpiTmaStore || p.epi_mode == kEpiTmaReduce;
         const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
         for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
             const TileCoord t = decode_unit(p, unit);
@@ -564,8 +564,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const int col0 = t.tn * BN + chunk * 32;
                     if (col0 >= p.N) break;           // warp-uniform
                     uint32_t v[32];
+                    __syncwarp();                      // tcgen05.ld is warp-collective
+                    const long long t_ld0 = clock64();
                     tmem_ld32_issue(tbase + chunk * 32, v);
                     tmem_ld_wait();
+                    t_ld += clock64() - t_ld0;
                     if (fuse && p.bias != nullptr) {
                         if (bias_vec && col0 + 32 <= p.N) {
 #pragma unroll
@@ -584,11 +587,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     if (use_tma) {
                         // The patch about to be overwritten must have been read by its TMA store.
-                        if (lane == 0 && in_flight == 2) {
-                            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                            in_flight = 1;
+                        const long long t_wg0 = clock64();
+                        if (lane == 0 && in_flight == p.epi_patches) {
+                            if (p.epi_patches == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                            else if (p.epi_patches == 4) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+                            else asm volatile("cp.async.bulk.wait_group.read 7;" ::: "memory");
+                            --in_flight;
                         }
                         __syncwarp();
+                        t_wg += clock64() - t_wg0;
                         uint8_t *dst = my_stage + patch * kEpiBufBytes + lane * 128;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
@@ -604,12 +611,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                             ++in_flight;
                         }
-                        patch ^= 1;
+                        if (++patch == p.epi_patches) patch = 0;
                     } else {
                         const int row = row0 + lane;
                         if (row < p.M) {
                             float *out = fuse ? p.C + static_cast<long long>(t.bt) * p.c_bstride + static_cast<long long>(row) * p.ldc
                                               : p.partial + (static_cast<long long>(cbatch) * p.M + row) * p.N;
+                            if (p.epi_mode == kEpiVectorStores && col0 + 32 <= p.N) {
+                                // Each lane owns one row: four 32-byte stores write whole sectors, no staging.
+                                float *dst = out + col0;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    float y[8];
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(v[8 * j + e]);
+                                    if (fuse && p.accumulate) {
+                                        float o[8];
+                                        asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                                     : "=f"(o[0]), "=f"(o[1]), "=f"(o[2]), "=f"(o[3]), "=f"(o[4]), "=f"(o[5]),
+                                                       "=f"(o[6]), "=f"(o[7])
+                                                     : "l"(dst + 8 * j));
+#pragma unroll
+                                        for (int e = 0; e < 8; ++e) y[e] += o[e];
+                                    }
+                                    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + 8 * j),
+                                                 "f"(y[0]), "f"(y[1]), "f"(y[2]), "f"(y[3]), "f"(y[4]), "f"(y[5]), "f"(y[6]),
+                                                 "f"(y[7])
+                                                 : "memory");
+                                }
+                                continue;
+                            }
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 if (col0 + j < p.N) {
@@ -628,7 +659,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ++acc_it;
         }
         if (use_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-        if (p.prof && warp == 2 + NS && lane == 0) atomicAdd(p.prof + 4, static_cast<unsigned long long>(waited));
+        if (p.prof && warp == 2 + NS && lane == 0) {
+            atomicAdd(p.prof + 4, static_cast<unsigned long long>(waited));
+            atomicAdd(p.prof + 7, static_cast<unsigned long long>(t_wg));
+            atomicAdd(p.prof + 1, static_cast<unsigned long long>(t_ld));
+        }
     }
 
     tc_fence_before();
@@ -791,10 +826,11 @@ int make_output_map(CUtensorMap *map, float *ptr, int64_t N, int64_t M, int64_t 
 
 struct Plan {
     int bn, bk, cg, stages, splits, tiles_m, tiles_n, grid;   // cg = CTAs per tile (1, or 2 = CTA pair)
+    int patches;                                              // epilogue staging patches per warp
     size_t smem;
 };
 
-constexpr size_t kFixedSmem = 1024 + kEpiBytes + kBarBytes;
+constexpr size_t kFixedSmemNoEpi = 1024 + kBarBytes;
 
 Plan make_plan(const GemmProblem &p, int sm_count) {
     Plan pl;
@@ -809,10 +845,22 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     const size_t raw = static_cast<size_t>(BM + pl.bn / pl.cg) * pl.bk * 4;
     const size_t stage = p.fast_tf32 ? raw : 2 * raw;
     const size_t budget = 227 * 1024;
-    pl.stages = static_cast<int>(std::min<size_t>(kMaxStages, (budget - kFixedSmem) / stage));
+    // Tiles with a short contraction spend their time in the epilogue: give it more TMA stores in
+    // flight (staging patches) and the main loop fewer stages.  Long contractions get the deepest pipeline.
+    const long long iters_per_tile = p.fold * ((p.K + pl.bk - 1) / pl.bk);
+    pl.patches = 2;   // measured: more patches (fewer stages) never helped
+    (void)iters_per_tile;
+    const int pt_env = env_int("MNI_B200_EPI_PATCHES", 0);
+    if (pt_env == 2 || pt_env == 4 || pt_env == 8) pl.patches = pt_env;
+    size_t fixed = kFixedSmemNoEpi + static_cast<size_t>(4 * pl.patches) * kEpiBufBytes;
+    while (pl.patches > 2 && (budget - fixed) / stage < 2) {
+        pl.patches /= 2;
+        fixed = kFixedSmemNoEpi + static_cast<size_t>(4 * pl.patches) * kEpiBufBytes;
+    }
+    pl.stages = static_cast<int>(std::min<size_t>(kMaxStages, (budget - fixed) / stage));
     const int st_env = env_int("MNI_B200_STAGES", 0);
     if (st_env >= 1 && st_env <= pl.stages) pl.stages = st_env;
-    pl.smem = kFixedSmem + static_cast<size_t>(pl.stages) * stage;
+    pl.smem = fixed + static_cast<size_t>(pl.stages) * stage;
     const int tile_m = BM * pl.cg;
     const int slots = std::max(1, sm_count / pl.cg);          // CTAs (or CTA pairs) that run at once
     pl.tiles_m = static_cast<int>((p.M + tile_m - 1) / tile_m);
@@ -920,7 +968,11 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     const bool tma_ok = (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && dst_ld % 4 == 0 && dst_bs % 4 == 0 &&
                         env_int("MNI_B200_NO_TMA_STORE", 0) == 0;
     k.epi_mode = kEpiPlainStores;
-    if (tma_ok) {
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(dst) & 31) == 0 && dst_ld % 8 == 0 && dst_bs % 8 == 0;
+    if (vec_ok && env_int("MNI_B200_EPI_VECTOR", 0) != 0) {
+        k.epi_mode = kEpiVectorStores;
+        tmC = tmA;
+    } else if (tma_ok) {
         rc = make_output_map(&tmC, dst, p.N, p.M, dst_batches, dst_ld, dst_bs);
         if (rc) return rc;
         k.epi_mode = (p.accumulate && pl.splits == 1) ? kEpiTmaReduce : kEpiTmaStore;
@@ -944,6 +996,7 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     k.b_d1 = static_cast<int>(p.B.bshape[1]);
     k.b_d2 = static_cast<int>(p.B.bshape[2]);
     k.stages = pl.stages;
+    k.epi_patches = pl.patches;
     k.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.A.k_major ? 0u : 1u) << 15) |
               ((p.B.k_major ? 0u : 1u) << 16) | (static_cast<uint32_t>(pl.bn >> 3) << 17) |
               (static_cast<uint32_t>((BM * pl.cg) >> 4) << 24);
