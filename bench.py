@@ -119,6 +119,9 @@ WORKLOADS = {
     "c5b16": Workload("c5b16", "skinny M=16, K=N=4096", (16, 4096), (4096, 4096)),
 }
 HBM_BOUND = ("c3", "c5b1", "c5b4", "c5b16")
+# DRAM bytes per forward launch from ncu captures of the same launch
+# (dram__bytes_read.sum + dram__bytes_write.sum; 3xTF32 build with CTA pairs).
+NCU_TRAFFIC_BYTES = {"c2": 34.04e6 + 19.30e6}
 
 
 def shard_workload(wl: Workload, rank: int, world: int) -> Workload:
@@ -369,7 +372,10 @@ def run_ours(args):
         achieved = wl.fwd_flops / (fwd_ms * 1e-3) / 1e12
         issued = achieved * (1 if args.precision == "tf32" else 3)
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "traffic": None, "kernel": "gemm_tc_kernel (forward GEMM launch, bias fused)",
+                    "traffic": NCU_TRAFFIC_BYTES.get(wl.name) if args.precision != "tf32" else None,
+                    "traffic_unit": "bytes per launch (ncu dram read+write)",
+                    "algorithmic_bytes": 4.0 * (np.prod(wl.a_shape) + np.prod(wl.b_shape) + np.prod(wl.out_shape)),
+                    "kernel": "gemm_tc_kernel (forward GEMM launch, bias fused)",
                     "issued_tflops": issued, "issued_frac": issued / peak,
                     "note": ("3xTF32 issues 3 MMAs per product: algorithmic ceiling = peak/3"
                              if args.precision != "tf32" else "single-pass TF32"),

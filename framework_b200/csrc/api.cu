@@ -427,6 +427,18 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
             rc = zero_or_bias_fill(c, da, a_elems, 1, nullptr, acc_da);
             if (rc) return rc;
         } else {
+            const bool skinny_dx = ((c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
+                                    ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 8)) &&
+                                   s.batch == 1 && g_batch == 1 && s.a_batch == 1 && s.b_batch == 1 &&
+                                   dc->stride[gn - 1] == 1 && b->stride[b->ndim - 1] == 1 && s.K > 1 &&
+                                   skinny_dx_supported(dc->ptr, dc->stride[gn - 2], b->ptr, b->stride[b->ndim - 2], s.M, s.N);
+            if (skinny_dx) {
+                if (!c.dry()) {
+                    rc = launch_skinny_dx(dc->ptr, dc->stride[gn - 2], b->ptr, b->stride[b->ndim - 2], da, s.K, acc_da,
+                                          s.M, s.N, s.K, c.stream);
+                    if (rc) return rc;
+                }
+            } else {
             int64_t ob[MNI_B200_MAX_DIMS];
             const int onb = broadcast_shape(dc->shape, gn - 2, b->shape, b->ndim - 2, ob);
             if (onb < 0) return fail(MNI_B200_ERR_BROADCAST, "dc and b batch shapes are not broadcastable");
@@ -439,6 +451,7 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
             Y.batch = s.b_batch;
             rc = grad_gemm(c, X, Y, s.M, s.K, s.N, ob, onb, *a, da, acc_da);
             if (rc) return rc;
+            }
         }
     }
 

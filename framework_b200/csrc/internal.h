@@ -90,7 +90,8 @@ size_t skinny_fwd_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count);
 int launch_skinny_fwd(const float *x, int64_t ldx, const float *W, int64_t ldw, float *y, int64_t ldy,
                       const float *bias, bool accumulate, int64_t M, int64_t N, int64_t K,
                       float *partial, int sm_count, cudaStream_t stream);
-//   dx[M,K] = dy[M,N] . W[K,N]^T                                    M <= 16
+//   dx[M,K] = dy[M,N] . W[K,N]^T                                    M <= 8
+bool skinny_dx_supported(const float *dy, int64_t lddy, const float *W, int64_t ldw, int64_t M, int64_t N);
 int launch_skinny_dx(const float *dy, int64_t lddy, const float *W, int64_t ldw, float *dx, int64_t lddx,
                      bool accumulate, int64_t M, int64_t N, int64_t K, cudaStream_t stream);
 //   dW[K,N] = x[M,K]^T . dy[M,N]                                     M <= 16

@@ -5,7 +5,7 @@
 //
 //   fwd : y[M,N]  = x[M,K] . W[K,N] (+bias)        W streamed once, split-K partials, fused finish
 //   dW  : dW[K,N] = x[M,K]^T . dy[M,N]             dW written once
-// (dx = dy . W^T is a K-major/K-major product and goes through the tensor-core kernel.)
+//   dx  : dx[M,K] = dy[M,N] . W[K,N]^T             W streamed once, one warp per two rows of W
 #include "internal.h"
 
 #include <algorithm>
@@ -227,6 +227,66 @@ skinny_dw_kernel(const float *__restrict__ x, long long ldx, const float *__rest
     }
 }
 
+// dx[M,K] = dy[M,N] . W[K,N]^T.  A warp owns kDxRows rows of W; its lanes walk the row 128 floats at
+// a time with 16-byte streaming loads, multiply with the matching dy slices (a few KB, served from
+// L1/L2) and a shuffle tree folds the 32 lane sums.  W is read exactly once.
+constexpr int kDxThreads = 256;
+constexpr int kDxRows = 2;
+template <int MT>
+__global__ void __launch_bounds__(kDxThreads)
+skinny_dx_kernel(const float *__restrict__ dy, long long lddy, const float *__restrict__ W, long long ldw,
+                 float *__restrict__ dx, long long lddx, int accumulate, int M, long long N, long long K) {
+    const int lane = threadIdx.x & 31;
+    const long long gw = static_cast<long long>(blockIdx.x) * (kDxThreads / 32) + (threadIdx.x >> 5);
+    const long long k0 = gw * kDxRows;
+    if (k0 >= K) return;
+    float acc[kDxRows][MT];
+#pragma unroll
+    for (int r = 0; r < kDxRows; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+    const float *w0 = W + k0 * ldw;
+    const bool row1 = k0 + 1 < K;
+    const float *w1 = row1 ? w0 + ldw : w0;
+    for (long long n = lane * 4; n < N; n += 256) {
+        const long long n2 = n + 128;
+        const bool second = n2 < N;
+        float4 wa = __ldcs(reinterpret_cast<const float4 *>(w0 + n));
+        float4 wb = __ldcs(reinterpret_cast<const float4 *>(w1 + n));
+        float4 wc = make_float4(0.f, 0.f, 0.f, 0.f), wd = wc;
+        if (second) {
+            wc = __ldcs(reinterpret_cast<const float4 *>(w0 + n2));
+            wd = __ldcs(reinterpret_cast<const float4 *>(w1 + n2));
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m < M) {
+                const float4 g = __ldg(reinterpret_cast<const float4 *>(dy + m * lddy + n));
+                acc[0][m] = fmaf(g.x, wa.x, fmaf(g.y, wa.y, fmaf(g.z, wa.z, fmaf(g.w, wa.w, acc[0][m]))));
+                acc[1][m] = fmaf(g.x, wb.x, fmaf(g.y, wb.y, fmaf(g.z, wb.z, fmaf(g.w, wb.w, acc[1][m]))));
+                if (second) {
+                    const float4 h = __ldg(reinterpret_cast<const float4 *>(dy + m * lddy + n2));
+                    acc[0][m] = fmaf(h.x, wc.x, fmaf(h.y, wc.y, fmaf(h.z, wc.z, fmaf(h.w, wc.w, acc[0][m]))));
+                    acc[1][m] = fmaf(h.x, wd.x, fmaf(h.y, wd.y, fmaf(h.z, wd.z, fmaf(h.w, wd.w, acc[1][m]))));
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kDxRows; ++r) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float v = acc[r][m];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+            if (lane == 0 && m < M && k0 + r < K) {
+                float *dst = dx + m * lddx + k0 + r;
+                *dst = accumulate ? *dst + v : v;
+            }
+        }
+    }
+}
+
 int pick_mt(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16; }
 
 struct FwdPlan { int splits; long long k_per; int strips; };
@@ -282,9 +342,28 @@ int launch_skinny_fwd(const float *x, int64_t ldx, const float *W, int64_t ldw, 
     return MNI_B200_OK;
 }
 
-int launch_skinny_dx(const float *, int64_t, const float *, int64_t, float *, int64_t, bool, int64_t, int64_t,
-                     int64_t, cudaStream_t) {
-    return fail(MNI_B200_ERR_ARG, "skinny dx runs on the tensor-core path");
+bool skinny_dx_supported(const float *dy, int64_t lddy, const float *W, int64_t ldw, int64_t M, int64_t N) {
+    return M >= 1 && M <= 8 && N % 4 == 0 && ldw % 4 == 0 && lddy % 4 == 0 &&
+           ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(dy)) & 15) == 0;
+}
+
+int launch_skinny_dx(const float *dy, int64_t lddy, const float *W, int64_t ldw, float *dx, int64_t lddx,
+                     bool accumulate, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+    const int mt = pick_mt(M);
+    const long long rows_per_block = (kDxThreads / 32) * kDxRows;
+    const unsigned blocks = static_cast<unsigned>((K + rows_per_block - 1) / rows_per_block);
+#define MNI_SKINNY_DX(MT)                                                                              \
+    case MT:                                                                                           \
+        skinny_dx_kernel<MT><<<blocks, kDxThreads, 0, stream>>>(dy, lddy, W, ldw, dx, lddx, accumulate ? 1 : 0, \
+                                                                (int)M, N, K);                         \
+        break;
+    switch (mt) {
+        MNI_SKINNY_DX(1) MNI_SKINNY_DX(2) MNI_SKINNY_DX(4) MNI_SKINNY_DX(8)
+        default: return fail(MNI_B200_ERR_ARG, "skinny dx handles at most 8 rows");
+    }
+#undef MNI_SKINNY_DX
+    MNI_LAUNCH_CHECK("skinny_dx_kernel");
+    return MNI_B200_OK;
 }
 
 int launch_skinny_dw(const float *x, int64_t ldx, const float *dy, int64_t lddy, float *dW, int64_t lddw,

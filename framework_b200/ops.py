@@ -107,6 +107,23 @@ def add_backward(grad: DeviceTensor, a_shape: Sequence[int], b_shape: Sequence[i
     return ga, gb
 
 
+def permute(a: DeviceTensor, dims: Sequence[int]) -> DeviceTensor:
+    """``ops::layout::permute``: a stride-only view sharing the storage (what the reference's CPU backend
+    does, ops/layout.rs:112-134); the matmul kernels read it in place."""
+    return a.permute(dims)
+
+
+def permute_backward(grad: DeviceTensor, dims: Sequence[int], orig_shape: Sequence[int]) -> DeviceTensor:
+    """``ops::layout::permute_backward`` (ops/layout.rs:198-212): the gradient of the permuted tensor, put
+    back into the original layout -- one device gather of the inverse-permuted view."""
+    if tuple(grad.shape) != tuple(orig_shape[d] for d in dims):
+        raise ValueError(f"grad has shape {grad.shape}, expected {tuple(orig_shape[d] for d in dims)}")
+    inv = [0] * len(dims)
+    for i, d in enumerate(dims):
+        inv[d] = i
+    return grad.permute(inv).contiguous()
+
+
 class Linear:
     """``Linear`` of src/nn.ts:8-26 over device tensors: y = x.W + b with W [in, out].
 

@@ -181,6 +181,22 @@ def test_attention_shaped_strided_k(F, oracle):
     _check_bwd(F, oracle, q, k, d_s, perm_b=[0, 1, 3, 2])
 
 
+def test_permute_backward_returns_the_original_layout(F, oracle):
+    """dK of the attention-shaped case: the gradient of K^T = permute(K, [0,1,3,2]) put back in K's layout
+    (ops/layout.rs:162-212), bit-exact (it only moves data)."""
+    rng = np.random.default_rng(24)
+    for shape, dims in (((2, 3, 40, 24), [0, 1, 3, 2]), ((5, 6, 7), [2, 0, 1]), ((9, 4), [1, 0])):
+        g = rng.standard_normal([shape[d] for d in dims], dtype=np.float32)
+        ref = oracle.permute_backward(oracle.HostTensor.from_array(g), dims, shape).numpy()
+        got = F.permute_backward(_dev(F, g), dims, shape)
+        assert got.is_contiguous() and got.shape == tuple(shape)
+        assert np.array_equal(got.numpy(), ref)
+    dev = _dev(F, rng.standard_normal((6, 8, 10), dtype=np.float32))
+    view = F.permute(dev, [1, 2, 0])
+    assert view.ptr == dev.ptr and view.strides == (10, 1, 80) and not view.is_contiguous()
+    assert np.array_equal(view.contiguous().numpy(), np.transpose(dev.numpy(), (1, 2, 0)))
+
+
 def test_head_split_view_with_two_batch_strides(F, oracle):
     """[B,S,H,D] -> permute(0,2,1,3): batch dims that do not collapse into one stride."""
     rng = np.random.default_rng(15)
