@@ -51,12 +51,17 @@ _SIGNATURES = {
     "mni_b200_version": (C.c_int, []),
     "mni_b200_last_error": (C.c_char_p, []),
     "mni_b200_matmul_fwd": (C.c_int, [C.POINTER(View), C.POINTER(View), C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "mni_b200_matmul_bias_gelu_fwd": (C.c_int, [C.POINTER(View), C.POINTER(View), C.c_void_p, C.c_void_p, C.c_void_p,
+                                                C.c_uint32, C.c_void_p]),
     "mni_b200_matmul_bwd": (C.c_int, [C.POINTER(View), C.POINTER(View), C.POINTER(View), C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_uint32, C.c_void_p]),
     "mni_b200_add_bias": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "mni_b200_add_bias_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_uint32, C.c_void_p]),
     "mni_b200_add_bias_bwd_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_uint32,
                                                 C.c_void_p]),
+    "mni_b200_bias_gelu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
+    "mni_b200_bias_gelu_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                         C.c_int64, C.c_uint32, C.c_void_p]),
     "mni_b200_contiguous": (C.c_int, [C.POINTER(View), C.c_void_p, C.c_void_p]),
     "mni_b200_workspace_set": (C.c_int, [C.c_void_p, C.c_size_t]),
     "mni_b200_workspace_query": (C.c_int, [C.POINTER(View), C.POINTER(View), C.c_uint32, C.POINTER(C.c_size_t)]),

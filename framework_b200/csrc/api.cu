@@ -325,6 +325,51 @@ int fwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, float *out
     return run_gemm(c, p);
 }
 
+// Forward with the bias + GELU epilogue: pre = a . b (optional output), out = gelu(pre + bias).
+int fwd_gelu_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const float *bias, float *pre,
+                  float *out) {
+    Shapes s;
+    int rc = analyse(a, b, s);
+    if (rc) return rc;
+    const int64_t rows = s.batch * s.M;
+    if (rows * s.N == 0) return MNI_B200_OK;
+    if (!bias || !out) return fail(MNI_B200_ERR_ARG, "bias and out must not be null");
+    const uint32_t saved_flags = c.flags;
+    c.flags &= ~static_cast<uint32_t>(MNI_B200_ACCUMULATE_C);
+    const bool skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
+                        ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 8);
+    if (s.K > 0 && !skinny) {
+        GemmProblem p;
+        rc = make_operand(c, *a, false, p.A);
+        if (rc) return rc;
+        rc = make_operand(c, *b, true, p.B);
+        if (rc) return rc;
+        p.A.batch = s.a_batch;
+        p.B.batch = s.b_batch;
+        p.M = s.M; p.N = s.N; p.K = s.K;
+        p.batch = s.batch;
+        p.C = pre; p.D = out;
+        p.ldc = s.N; p.c_bstride = s.M * s.N;
+        p.bias = bias;
+        p.fast_tf32 = (c.flags & MNI_B200_PRECISION_TF32) != 0;
+        p.force_splits = static_cast<int>((c.flags >> 16) & 0xffu);
+        if (gemm_tc_can_fuse_activation(p, c.st->sm_count)) {
+            rc = run_gemm(c, p);
+            c.flags = saved_flags;
+            return rc;
+        }
+    }
+    // Not fusable (split-K, skinny rows, unaligned rows): the product first, then the pointwise kernel.
+    float *tmp = pre;
+    size_t off = 0;
+    if (!tmp) off = c.arena.reserve(static_cast<size_t>(rows * s.N) * sizeof(float));
+    if (!tmp && !c.dry()) tmp = c.at(off);
+    rc = fwd_body(c, a, b, c.dry() && !tmp ? reinterpret_cast<float *>(static_cast<uintptr_t>(256)) : tmp, nullptr);
+    c.flags = saved_flags;
+    if (rc || c.dry()) return rc;
+    return launch_bias_gelu(tmp, bias, out, rows, s.N, c.stream);
+}
+
 // ------------------------------------------------------------------ backward
 // One gradient: G[ob.., R, Cn] = X . Y (a GEMM over `kdim`) reduced to `target`'s shape.
 //   X supplies the rows, Y the columns; both already as Operands with flat batch counts.
@@ -540,6 +585,14 @@ int mni_b200_matmul_fwd(const mni_b200_view *a, const mni_b200_view *b, float *c
     return with_scratch(flags, stream, [&](Call &call) { return fwd_body(call, a, b, c, bias); });
 }
 
+int mni_b200_matmul_bias_gelu_fwd(const mni_b200_view *a, const mni_b200_view *b, const float *bias, float *pre,
+                                  float *out, uint32_t flags, void *stream) {
+    Shapes s;
+    int rc = analyse(a, b, s);
+    if (rc) return rc;
+    return with_scratch(flags, stream, [&](Call &call) { return fwd_gelu_body(call, a, b, bias, pre, out); });
+}
+
 int mni_b200_matmul_bwd(const mni_b200_view *a, const mni_b200_view *b, const mni_b200_view *dc, float *da,
                         float *db, float *dbias, uint32_t flags, void *stream) {
     Shapes s;
@@ -579,6 +632,31 @@ int mni_b200_add_bias_bwd(const float *dy, float *d_y, float *dbias, int64_t row
         const size_t poff = c.arena.reserve(colsum_partial_bytes(rows, n, c.st->sm_count));
         if (c.dry()) return MNI_B200_OK;
         return launch_colsum(dy, n, dbias, rows, n, acc, c.at(poff), c.st->sm_count, c.stream);
+    });
+}
+
+int mni_b200_bias_gelu(const float *x, const float *bias, float *out, int64_t rows, int64_t n, void *stream) {
+    if (rows < 0 || n < 0) return fail(MNI_B200_ERR_ARG, "negative extent");
+    if (rows * n == 0) return MNI_B200_OK;
+    if (!x || !bias || !out) return fail(MNI_B200_ERR_ARG, "null pointer");
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    return launch_bias_gelu(x, bias, out, rows, n, static_cast<cudaStream_t>(stream));
+}
+
+int mni_b200_bias_gelu_bwd(const float *grad, const float *x, const float *bias, float *dx, float *dbias,
+                           int64_t rows, int64_t n, uint32_t flags, void *stream) {
+    if (rows < 0 || n < 0) return fail(MNI_B200_ERR_ARG, "negative extent");
+    if (rows * n > 0 && (!grad || !x || !bias || !dx)) return fail(MNI_B200_ERR_ARG, "null pointer");
+    if (n > 0 && !dbias) return fail(MNI_B200_ERR_ARG, "dbias is null");
+    return with_scratch(flags, stream, [&](Call &c) -> int {
+        const bool acc = (flags & MNI_B200_ACCUMULATE_DBIAS) != 0;
+        if (n == 0) return MNI_B200_OK;
+        if (rows == 0) return zero_or_bias_fill(c, dbias, 1, n, nullptr, acc);
+        const size_t poff = c.arena.reserve(colsum_partial_bytes(rows, n, c.st->sm_count));
+        if (c.dry()) return MNI_B200_OK;
+        return launch_bias_gelu_bwd(grad, x, bias, dx, dbias, rows, n, acc, c.at(poff), c.st->sm_count, c.stream);
     });
 }
 

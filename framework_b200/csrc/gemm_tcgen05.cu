@@ -68,6 +68,8 @@ struct KParams {
     float *partial;            // split-K: [split][batch][M][N]
     const float *bias;
     int accumulate;
+    int act;                   // 1: also emit gelu(acc + bias) through the second output map
+    int store_pre;             // act mode: write the raw product through the first map as well
     unsigned int *err;
     unsigned long long *prof;  // optional role wait counters (null = off)
 };
@@ -236,6 +238,12 @@ __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// gelu(v) = 0.5 v (1 + tanh(sqrt(2/pi) (v + 0.044715 v^3)))   (kernels/fused_ops.cu:66-82)
+__device__ __forceinline__ float gelu_tanh_f(float v) {
+    const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    return 0.5f * v * (1.0f + tanhf(inner));
+}
+
 struct TileCoord {
     int bt, tm, tn, split, it0, it1;
 };
@@ -300,7 +308,8 @@ __device__ __forceinline__ void load_operand(int mode, uint32_t dst, const CUten
 template <int BN, int BK, bool FAST, int NS, int CG>
 __global__ void __launch_bounds__(32 * (6 + NS), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const KParams p) {
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
+               const KParams p) {
     static_assert(CG == 1 || (CG == 2 && !FAST), "CTA pairs are built for the 3xTF32 mode only");
     constexpr int BNL = BN / CG;                           // B rows staged by this CTA
     constexpr uint32_t A_BYTES = BM * BK * 4;
@@ -569,26 +578,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tmem_ld32_issue(tbase + chunk * 32, v);
                     tmem_ld_wait();
                     t_ld += clock64() - t_ld0;
-                    if (fuse && p.bias != nullptr) {
-                        if (bias_vec && col0 + 32 <= p.N) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + col0) + j);
-                                v[4 * j + 0] = __float_as_uint(__uint_as_float(v[4 * j + 0]) + b.x);
-                                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + b.y);
-                                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + b.z);
-                                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + b.w);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.N) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldg(p.bias + col0 + j));
-                        }
-                    }
-                    if (use_tma) {
-                        // The patch about to be overwritten must have been read by its TMA store.
+                    // Stages the 32 values of this lane's row into the warp's next patch and hands the
+                    // patch to the TMA unit (store, or reduce-add for C += ...).
+                    auto emit = [&](const CUtensorMap *map, bool reduce) {
                         const long long t_wg0 = clock64();
-                        if (lane == 0 && in_flight == p.epi_patches) {
+                        if (lane == 0 && in_flight == p.epi_patches) {   // the patch must have been read by its store
                             if (p.epi_patches == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                             else if (p.epi_patches == 4) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
                             else asm volatile("cp.async.bulk.wait_group.read 7;" ::: "memory");
@@ -606,12 +600,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         __syncwarp();
                         if (lane == 0) {
                             const uint32_t src = smem_u32(my_stage + patch * kEpiBufBytes);
-                            if (p.epi_mode == kEpiTmaReduce && fuse) tma_reduce_add_5d(&tmC, src, col0, row0, cbatch);
-                            else tma_store_5d(&tmC, src, col0, row0, cbatch);
+                            if (reduce) tma_reduce_add_5d(map, src, col0, row0, cbatch);
+                            else tma_store_5d(map, src, col0, row0, cbatch);
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                             ++in_flight;
                         }
                         if (++patch == p.epi_patches) patch = 0;
+                    };
+                    const bool do_act = fuse && p.act != 0;          // host guarantees use_tma in this mode
+                    if (do_act && p.store_pre) emit(&tmC, false);    // the raw product, what the tape saves
+                    if (fuse && p.bias != nullptr) {
+                        if (bias_vec && col0 + 32 <= p.N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + col0) + j);
+                                v[4 * j + 0] = __float_as_uint(__uint_as_float(v[4 * j + 0]) + b.x);
+                                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + b.y);
+                                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + b.z);
+                                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + b.w);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.N) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldg(p.bias + col0 + j));
+                        }
+                    }
+                    if (do_act) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(gelu_tanh_f(__uint_as_float(v[j])));
+                        emit(&tmD, false);
+                    } else if (use_tma) {
+                        emit(&tmC, p.epi_mode == kEpiTmaReduce && fuse);
                     } else {
                         const int row = row0 + lane;
                         if (row < p.M) {
@@ -888,7 +907,7 @@ uint32_t desc_hi_bits(uint32_t sbo_bytes, uint32_t layout_type) {
 
 template <int BN, int BK, bool FAST, int NS, int CG>
 cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
-                           const KParams &k, cudaStream_t stream) {
+                           const CUtensorMap &tmD, const KParams &k, cudaStream_t stream) {
     static std::once_flag once;
     static cudaError_t attr = cudaSuccess;
     std::call_once(once, [] {
@@ -908,7 +927,7 @@ cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtenso
     attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = CG == 2 ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK, FAST, NS, CG>, tmA, tmB, tmC, k);
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK, FAST, NS, CG>, tmA, tmB, tmC, tmD, k);
 }
 
 }  // namespace
@@ -939,6 +958,13 @@ int read_role_waits(uint64_t out[8], int reset) {
     return MNI_B200_OK;
 }
 
+bool gemm_tc_can_fuse_activation(const GemmProblem &p, int sm_count) {
+    const Plan pl = make_plan(p, sm_count);
+    auto aligned = [&](const float *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    return pl.splits == 1 && p.ldc % 4 == 0 && p.c_bstride % 4 == 0 && aligned(p.D) && (p.C == nullptr || aligned(p.C)) &&
+           env_int("MNI_B200_NO_TMA_STORE", 0) == 0 && env_int("MNI_B200_EPI_VECTOR", 0) == 0;
+}
+
 size_t gemm_tc_partial_bytes(const GemmProblem &p, int sm_count) {
     const Plan pl = make_plan(p, sm_count);
     if (pl.splits <= 1) return 0;
@@ -954,7 +980,9 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
         return fail(MNI_B200_ERR_WORKSPACE, "split-K launch without partial storage");
 
     KParams k{};
-    CUtensorMap tmA, tmB, tmC;
+    CUtensorMap tmA, tmB, tmC, tmD;
+    if (p.D != nullptr && !gemm_tc_can_fuse_activation(p, sm_count))
+        return fail(MNI_B200_ERR_ARG, "fused activation requested for a problem that cannot carry it");
     int rc = make_operand_map(&tmA, p.A, BM, pl.bk, &k.a_mode);
     if (rc) return rc;
     rc = make_operand_map(&tmB, p.B, pl.bn / pl.cg, pl.bk, &k.b_mode);
@@ -972,12 +1000,23 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     if (vec_ok && env_int("MNI_B200_EPI_VECTOR", 0) != 0) {
         k.epi_mode = kEpiVectorStores;
         tmC = tmA;
-    } else if (tma_ok) {
-        rc = make_output_map(&tmC, dst, p.N, p.M, dst_batches, dst_ld, dst_bs);
-        if (rc) return rc;
+    } else if (tma_ok && (dst != nullptr || p.D != nullptr)) {
+        if (dst != nullptr) {
+            rc = make_output_map(&tmC, dst, p.N, p.M, dst_batches, dst_ld, dst_bs);
+            if (rc) return rc;
+        } else {
+            tmC = tmA;
+        }
         k.epi_mode = (p.accumulate && pl.splits == 1) ? kEpiTmaReduce : kEpiTmaStore;
     } else {
         tmC = tmA;   // unused by the plain-store epilogue, but must be a valid object
+    }
+    tmD = tmC;
+    if (p.D != nullptr) {
+        rc = make_output_map(&tmD, p.D, p.N, p.M, p.batch, p.ldc, p.c_bstride);
+        if (rc) return rc;
+        k.act = 1;
+        k.store_pre = p.C != nullptr ? 1 : 0;
     }
 
     k.M = static_cast<int>(p.M);
@@ -1024,12 +1063,12 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     const int split_warps = env_int("MNI_B200_SPLIT_WARPS", 8);
 #define MNI_VARIANT(BN_, BK_)                                                                         \
     if (pl.cg == 1 && pl.bn == BN_ && pl.bk == BK_) {                                                 \
-        if (p.fast_tf32) e = launch_variant<BN_, BK_, true, 4, 1>(pl, tmA, tmB, tmC, k, stream);      \
-        else if (split_warps == 8) e = launch_variant<BN_, BK_, false, 8, 1>(pl, tmA, tmB, tmC, k, stream); \
-        else e = launch_variant<BN_, BK_, false, 4, 1>(pl, tmA, tmB, tmC, k, stream);                 \
+        if (p.fast_tf32) e = launch_variant<BN_, BK_, true, 4, 1>(pl, tmA, tmB, tmC, tmD, k, stream);      \
+        else if (split_warps == 8) e = launch_variant<BN_, BK_, false, 8, 1>(pl, tmA, tmB, tmC, tmD, k, stream); \
+        else e = launch_variant<BN_, BK_, false, 4, 1>(pl, tmA, tmB, tmC, tmD, k, stream);                 \
     }
-    if (pl.cg == 2 && pl.bk == 16) e = launch_variant<256, 16, false, 8, 2>(pl, tmA, tmB, tmC, k, stream);
-    if (pl.cg == 2 && pl.bk == 32) e = launch_variant<256, 32, false, 8, 2>(pl, tmA, tmB, tmC, k, stream);
+    if (pl.cg == 2 && pl.bk == 16) e = launch_variant<256, 16, false, 8, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
+    if (pl.cg == 2 && pl.bk == 32) e = launch_variant<256, 32, false, 8, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
     MNI_VARIANT(64, 16) MNI_VARIANT(64, 32) MNI_VARIANT(128, 16) MNI_VARIANT(128, 32) MNI_VARIANT(256, 16)
     MNI_VARIANT(256, 32)
 #undef MNI_VARIANT

@@ -62,6 +62,8 @@ struct GemmProblem {
     bool accumulate = false;       // C += ...
     bool fast_tf32 = false;        // one TF32 pass instead of the 3-pass split
     int force_splits = 0;          // tests
+    // Optional second output D = gelu(C + bias) written by the same epilogue (C itself is skipped if null).
+    float *D = nullptr;
 };
 
 // Scratch layout handed to launchers (all device memory, owned by api.cu).
@@ -78,6 +80,9 @@ size_t gemm_tc_partial_bytes(const GemmProblem &p, int sm_count);
 // `partial` must hold gemm_tc_partial_bytes() bytes when that is non-zero.
 int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int sm_count,
                    cudaStream_t stream);
+// True if the fused second output (GemmProblem::D) can be produced for this problem: no split-K and a
+// 16-byte aligned row pitch.  Otherwise the caller runs the GEMM and the pointwise kernel separately.
+bool gemm_tc_can_fuse_activation(const GemmProblem &p, int sm_count);
 
 // Diagnostics: copies the 8 role wait counters of the current device (collected only while
 // MNI_B200_ROLE_WAITS=1 is set in the environment) and optionally clears them.
@@ -105,6 +110,11 @@ size_t colsum_partial_bytes(int64_t rows, int64_t n, int sm_count);
 int launch_colsum(const float *dy, int64_t ld, float *out, int64_t rows, int64_t n, bool accumulate,
                   float *partial, int sm_count, cudaStream_t stream);
 int launch_copy(const float *src, float *dst, int64_t n, cudaStream_t stream);
+// out = gelu_tanh(x + bias[col]);  dx = grad * gelu'(x + bias), dbias = column sums of dx (partial: colsum_partial_bytes)
+int launch_bias_gelu(const float *x, const float *bias, float *out, int64_t rows, int64_t n, cudaStream_t stream);
+int launch_bias_gelu_bwd(const float *grad, const float *x, const float *bias, float *dx, float *dbias,
+                         int64_t rows, int64_t n, bool accumulate, float *partial, int sm_count,
+                         cudaStream_t stream);
 // dst[row-major, ld_dst on the last dim] = gather of a strided view
 int launch_pack(const mni_b200_view &src, float *dst, int64_t ld_dst, cudaStream_t stream);
 // device-side utils::unbroadcast: out[orig] (+)= sum over broadcast dims of grad[gshape]

@@ -83,6 +83,95 @@ __global__ void colsum_final_kernel(const float *__restrict__ partial, float *__
     out[j] = accumulate ? out[j] + s : s;
 }
 
+// ---- bias + GELU (tanh form), the fused pointwise op that follows the MLP up-projection --------
+// gelu(v) = 0.5 v (1 + tanh(sqrt(2/pi) (v + 0.044715 v^3))), v = x + bias   (kernels/fused_ops.cu:66-82)
+__device__ __forceinline__ float gelu_tanh(float v) {
+    const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    return 0.5f * v * (1.0f + tanhf(inner));
+}
+// d gelu / d v                                                             (kernels/fused_ops.cu:96-103)
+__device__ __forceinline__ float gelu_tanh_grad(float v) {
+    const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    const float th = tanhf(inner);
+    const float sech2 = 1.0f - th * th;
+    const float d_inner = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * v * v);
+    return 0.5f * (1.0f + th) + 0.5f * v * sech2 * d_inner;
+}
+
+__global__ void bias_gelu_vec_kernel(const float4 *__restrict__ x, const float4 *__restrict__ bias,
+                                     float4 *__restrict__ out, long long total4, int n4) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total4;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const float4 b = __ldg(bias + static_cast<int>(i % n4));
+        const float4 v = x[i];
+        out[i] = make_float4(gelu_tanh(v.x + b.x), gelu_tanh(v.y + b.y), gelu_tanh(v.z + b.z), gelu_tanh(v.w + b.w));
+    }
+}
+__global__ void bias_gelu_scalar_kernel(const float *__restrict__ x, const float *__restrict__ bias,
+                                        float *__restrict__ out, long long total, long long n) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        out[i] = gelu_tanh(x[i] + __ldg(bias + i % n));
+}
+
+// Backward, stage 1: dx = grad * gelu'(x + bias) written once, and the column sums of dx over a slab of
+// rows (same block shape and fixed summation order as colsum_partial_kernel; no atomics).
+__global__ void bias_gelu_bwd_partial_kernel(const float *__restrict__ grad, const float *__restrict__ x,
+                                             const float *__restrict__ bias, float *__restrict__ dx,
+                                             float *__restrict__ partial, long long rows, long long n,
+                                             long long rows_per) {
+    __shared__ float4 red[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long col = (static_cast<long long>(blockIdx.x) * 32 + lane) * 4;
+    const long long r0 = blockIdx.y * rows_per;
+    const long long r1 = min(rows, r0 + rows_per);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const bool vec = ((n & 3) == 0) && col + 3 < n &&
+                     (((reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(x) |
+                        reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(bias)) & 15) == 0);
+    if (col < n) {
+        float b[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int e = 0; e < 4; ++e)
+            if (col + e < n) b[e] = __ldg(bias + col + e);
+        for (long long r = r0 + warp; r < r1; r += 8) {
+            const long long off = r * n + col;
+            if (vec) {
+                const float4 g = __ldg(reinterpret_cast<const float4 *>(grad + off));
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(x + off));
+                float4 d;
+                d.x = g.x * gelu_tanh_grad(v.x + b[0]);
+                d.y = g.y * gelu_tanh_grad(v.y + b[1]);
+                d.z = g.z * gelu_tanh_grad(v.z + b[2]);
+                d.w = g.w * gelu_tanh_grad(v.w + b[3]);
+                *reinterpret_cast<float4 *>(dx + off) = d;
+                acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+            } else {
+                float d[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int e = 0; e < 4; ++e) {
+                    if (col + e < n) {
+                        d[e] = __ldg(grad + off + e) * gelu_tanh_grad(__ldg(x + off + e) + b[e]);
+                        dx[off + e] = d[e];
+                    }
+                }
+                acc.x += d[0]; acc.y += d[1]; acc.z += d[2]; acc.w += d[3];
+            }
+        }
+    }
+    red[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && col < n) {
+        float4 s = red[0][lane];
+        for (int w = 1; w < 8; ++w) {
+            s.x += red[w][lane].x; s.y += red[w][lane].y; s.z += red[w][lane].z; s.w += red[w][lane].w;
+        }
+        float *o = partial + static_cast<long long>(blockIdx.y) * n + col;
+        o[0] = s.x;
+        if (col + 1 < n) o[1] = s.y;
+        if (col + 2 < n) o[2] = s.z;
+        if (col + 3 < n) o[3] = s.w;
+    }
+}
+
 struct PackArgs {
     int nd;
     long long shape[kMaxDims];
@@ -184,6 +273,38 @@ int launch_colsum(const float *dy, int64_t ld, float *out, int64_t rows, int64_t
     colsum_partial_kernel<<<grid, 256, 0, stream>>>(dy, ld, partial, rows, n, rows_per);
     MNI_LAUNCH_CHECK("colsum_partial_kernel");
     colsum_final_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(partial, out, n, slabs,
+                                                                                  accumulate ? 1 : 0);
+    MNI_LAUNCH_CHECK("colsum_final_kernel");
+    return MNI_B200_OK;
+}
+
+int launch_bias_gelu(const float *x, const float *bias, float *out, int64_t rows, int64_t n,
+                     cudaStream_t stream) {
+    const long long total = static_cast<long long>(rows) * n;
+    if (total == 0) return MNI_B200_OK;
+    const bool vec = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
+                                       reinterpret_cast<uintptr_t>(bias)) & 15) == 0;
+    if (vec) {
+        bias_gelu_vec_kernel<<<grid_for(total / 4, 256), 256, 0, stream>>>(
+            reinterpret_cast<const float4 *>(x), reinterpret_cast<const float4 *>(bias),
+            reinterpret_cast<float4 *>(out), total / 4, static_cast<int>(n / 4));
+    } else {
+        bias_gelu_scalar_kernel<<<grid_for(total, 256), 256, 0, stream>>>(x, bias, out, total, n);
+    }
+    MNI_LAUNCH_CHECK("bias_gelu");
+    return MNI_B200_OK;
+}
+
+int launch_bias_gelu_bwd(const float *grad, const float *x, const float *bias, float *dx, float *dbias,
+                         int64_t rows, int64_t n, bool accumulate, float *partial, int sm_count,
+                         cudaStream_t stream) {
+    if (n == 0 || rows == 0) return MNI_B200_OK;
+    const int slabs = colsum_slabs(rows, n, sm_count);
+    const long long rows_per = (rows + slabs - 1) / slabs;
+    dim3 grid(static_cast<unsigned>((n + 127) / 128), static_cast<unsigned>(slabs));
+    bias_gelu_bwd_partial_kernel<<<grid, 256, 0, stream>>>(grad, x, bias, dx, partial, rows, n, rows_per);
+    MNI_LAUNCH_CHECK("bias_gelu_bwd_partial_kernel");
+    colsum_final_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(partial, dbias, n, slabs,
                                                                                   accumulate ? 1 : 0);
     MNI_LAUNCH_CHECK("colsum_final_kernel");
     return MNI_B200_OK;

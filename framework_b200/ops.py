@@ -107,6 +107,46 @@ def add_backward(grad: DeviceTensor, a_shape: Sequence[int], b_shape: Sequence[i
     return ga, gb
 
 
+def bias_gelu(x: DeviceTensor, bias: DeviceTensor) -> DeviceTensor:
+    """``ops::fused::bias_gelu`` (ops/fused.rs:279-314): gelu(x + bias) with bias over the last dim."""
+    if bias.ndim != 1 or x.ndim < 1 or x.shape[-1] != bias.shape[0]:
+        raise ValueError("bias must be a [C] vector matching x's last dim")
+    x, bias = x.contiguous(), bias.contiguous()
+    out = DeviceTensor.empty(x.shape, x.storage.device)
+    n = x.shape[-1]
+    _lib.check(_lib.lib().mni_b200_bias_gelu(x.ptr, bias.ptr, out.ptr, shape_size(x.shape[:-1]), n, current_stream()))
+    return out
+
+
+def bias_gelu_backward(grad: DeviceTensor, x: DeviceTensor, bias: DeviceTensor, *,
+                       flags: int = 0) -> Tuple[DeviceTensor, DeviceTensor]:
+    """``ops::fused::bias_gelu_backward`` (ops/fused.rs:354-392) -> (dx, dbias)."""
+    if tuple(grad.shape) != tuple(x.shape) or bias.shape != (x.shape[-1],):
+        raise ValueError("grad must have x's shape and bias must be [C]")
+    g, x, bias = grad.contiguous(), x.contiguous(), bias.contiguous()
+    dx = DeviceTensor.empty(x.shape, x.storage.device)
+    dbias = DeviceTensor.empty(bias.shape, x.storage.device)
+    n = x.shape[-1]
+    _lib.check(_lib.lib().mni_b200_bias_gelu_bwd(g.ptr, x.ptr, bias.ptr, dx.ptr, dbias.ptr,
+                                                 shape_size(x.shape[:-1]), n, flags, current_stream()))
+    return dx, dbias
+
+
+def matmul_bias_gelu(a: DeviceTensor, b: DeviceTensor, bias: DeviceTensor, *, flags: int = 0,
+                     want_pre: bool = True) -> Tuple[Optional[DeviceTensor], DeviceTensor]:
+    """matmul followed by bias_gelu in one GEMM launch -> (pre = a.b or None, out = gelu(pre + bias))."""
+    oshape = _matmul_out_shape(a, b)
+    if bias.ndim != 1 or bias.shape[0] != oshape[-1] or not bias.is_contiguous():
+        raise ValueError("bias must be a contiguous [N] vector")
+    dev = a.storage.device
+    pre = DeviceTensor.empty(oshape, dev) if want_pre else None
+    out = DeviceTensor.empty(oshape, dev)
+    va, vb = a.view_struct(), b.view_struct()
+    _lib.check(_lib.lib().mni_b200_matmul_bias_gelu_fwd(va, vb, bias.ptr, pre.ptr if pre is not None else None,
+                                                        out.ptr, flags, current_stream()))
+    return pre, out
+
+
 def permute(a: DeviceTensor, dims: Sequence[int]) -> DeviceTensor:
     """``ops::layout::permute``: a stride-only view sharing the storage (what the reference's CPU backend
     does, ops/layout.rs:112-134); the matmul kernels read it in place."""

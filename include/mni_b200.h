@@ -97,6 +97,16 @@ MNI_B200_API int mni_b200_matmul_fwd(const mni_b200_view *a, const mni_b200_view
                         const float *bias, uint32_t flags, void *stream);
 
 /*
+ * Forward with the bias + GELU epilogue (the MLP up-projection): one call for what the reference runs
+ * as matmul (ops/matmul.rs:83-197) followed by bias_gelu (ops/fused.rs:279-314):
+ *   pre[batch..., M, N] = a . b            (written only if pre != NULL; it is what the tape saves)
+ *   out[batch..., M, N] = gelu(pre + bias[N])
+ * Both outputs leave the GEMM epilogue in the same pass over the accumulator.
+ */
+MNI_B200_API int mni_b200_matmul_bias_gelu_fwd(const mni_b200_view *a, const mni_b200_view *b, const float *bias,
+                                               float *pre, float *out, uint32_t flags, void *stream);
+
+/*
  * Backward.  Replaces ops/matmul.rs:224-255: both transpose_last2 calls
  * (:231, :242), both matmul_no_grad calls (:232, :243) and the device->host
  * unbroadcast round trips (:234-240, :245-251).
@@ -128,6 +138,22 @@ MNI_B200_API int mni_b200_add_bias(const float *y, const float *bias, float *out
  */
 MNI_B200_API int mni_b200_add_bias_bwd(const float *dy, float *d_y, float *dbias, int64_t rows, int64_t n,
                           uint32_t flags, void *stream);
+
+/*
+ * Fused bias + GELU (tanh form), the pointwise op that follows the MLP up-projection.  Replaces the
+ * bias_gelu_forward_f32 launch of ops/fused.rs:279-314 (kernels/fused_ops.cu:66-82):
+ *   out[r, j] = gelu(x[r, j] + bias[j]).
+ */
+MNI_B200_API int mni_b200_bias_gelu(const float *x, const float *bias, float *out, int64_t rows, int64_t n,
+                                    void *stream);
+
+/*
+ * Backward of bias + GELU.  Replaces ops/fused.rs:354-392 (kernels/fused_ops.cu:84-110, whose dbias is an
+ * atomicAdd in arbitrary order): dx = grad * gelu'(x + bias) and dbias[j] = sum over rows of dx[r, j],
+ * summed in a fixed order.  MNI_B200_ACCUMULATE_DBIAS adds into dbias.
+ */
+MNI_B200_API int mni_b200_bias_gelu_bwd(const float *grad, const float *x, const float *bias, float *dx,
+                                        float *dbias, int64_t rows, int64_t n, uint32_t flags, void *stream);
 
 /*
  * Same result as mni_b200_add_bias_bwd, for callers that must never see this library

@@ -26,6 +26,7 @@
 #include <stddef.h>
 #include <stdint.h>
 #include <stdlib.h>
+#include <math.h>
 #include <string.h>
 #ifdef _OPENMP
 #include <omp.h>
@@ -303,6 +304,34 @@ void oracle_permute_bwd(const float *grad, const int64_t *g_shape, int nd,
         for (int d = 0; d < nd; ++d) { coord[d] = rem / sstr[d]; rem %= sstr[d]; }
         for (int d = 0; d < nd; ++d) oi += coord[inv[d]] * ostr[d];
         out[oi] = grad[i];
+    }
+}
+
+/* ops/fused.rs:251-277  fused bias + GELU (tanh form), CPU backend: the constant is the Rust
+ * literal 0.7978845608_f32, evaluated in f32 exactly as written there. */
+void oracle_bias_gelu(const float *x, const float *bias, float *out, int64_t total, int64_t c) {
+    for (int64_t i = 0; i < total; ++i) {
+        const float val = x[i] + bias[i % c];
+        const float inner = 0.7978845608f * (val + 0.044715f * val * val * val);
+        out[i] = 0.5f * val * (1.0f + tanhf(inner));
+    }
+}
+
+/* ops/fused.rs:317-352  backward: dx = grad * gelu'(x + bias); dbias[j] += dx in ascending row order. */
+void oracle_bias_gelu_bwd(const float *grad, const float *x, const float *bias, float *dx, float *dbias,
+                          int64_t total, int64_t c) {
+    for (int64_t j = 0; j < c; ++j) dbias[j] = 0.0f;
+    for (int64_t i = 0; i < total; ++i) {
+        const int64_t j = i % c;
+        const float val = x[i] + bias[j];
+        const float inner = 0.7978845608f * (val + 0.044715f * val * val * val);
+        const float th = tanhf(inner);
+        const float sech2 = 1.0f - th * th;
+        const float d_inner = 0.7978845608f * (1.0f + 3.0f * 0.044715f * val * val);
+        const float dgelu = 0.5f * (1.0f + th) + 0.5f * val * sech2 * d_inner;
+        const float g = grad[i] * dgelu;
+        dx[i] = g;
+        dbias[j] += g;
     }
 }
 

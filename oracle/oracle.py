@@ -184,6 +184,25 @@ def add_backward(grad: HostTensor, a_shape: Sequence[int], b_shape: Sequence[int
             HostTensor(db, tuple(b_shape), _row_major(b_shape)))
 
 
+def bias_gelu(x: HostTensor, bias: HostTensor) -> HostTensor:
+    """ops/fused.rs:251-277 (CPU backend)."""
+    x, bias = contiguous(x), contiguous(bias)
+    out = np.empty(_shape_size(x.shape), np.float32)
+    lib().oracle_bias_gelu(_fp(x.data), _fp(bias.data), _fp(out), C.c_int64(_shape_size(x.shape)),
+                           C.c_int64(x.shape[-1]))
+    return HostTensor(out, tuple(x.shape), _row_major(x.shape))
+
+
+def bias_gelu_backward(grad: HostTensor, x: HostTensor, bias: HostTensor):
+    """ops/fused.rs:317-352 (CPU backend) -> (dx, dbias)."""
+    g, x, bias = contiguous(grad), contiguous(x), contiguous(bias)
+    dx = np.empty(_shape_size(x.shape), np.float32)
+    db = np.empty(x.shape[-1], np.float32)
+    lib().oracle_bias_gelu_bwd(_fp(g.data), _fp(x.data), _fp(bias.data), _fp(dx), _fp(db),
+                               C.c_int64(_shape_size(x.shape)), C.c_int64(x.shape[-1]))
+    return HostTensor(dx, tuple(x.shape), _row_major(x.shape)), HostTensor(db, (x.shape[-1],), (1,))
+
+
 def matmul_contig_raw(a: np.ndarray, b: np.ndarray, out: np.ndarray, batch: int, a_batch: int,
                       b_batch: int, m: int, k: int, n: int, threads: int) -> None:
     """The bare loop nest of ops/matmul.rs:54-70 on caller-owned buffers (bench baseline)."""
