@@ -310,7 +310,6 @@ __global__ void __launch_bounds__(32 * (6 + NS), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
                const KParams p) {
-    static_assert(CG == 1 || (CG == 2 && !FAST), "CTA pairs are built for the 3xTF32 mode only");
     constexpr int BNL = BN / CG;                           // B rows staged by this CTA
     constexpr uint32_t A_BYTES = BM * BK * 4;
     constexpr uint32_t B_BYTES = BNL * BK * 4;
@@ -346,12 +345,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(bar_full + 8u * s, 1);
-            mbar_init(bar_xform + 8u * s, CG * 32 * NS);   // split threads of both CTAs arrive on the leader's
+            mbar_init(bar_xform + 8u * s, CG * NS);        // one arrival per split warp, of both CTAs for a pair
             mbar_init(bar_empty + 8u * s, 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_acc_full + 8u * i, 1);
-            mbar_init(bar_acc_empty + 8u * i, CG * 128);   // epilogue threads of both CTAs arrive on the leader's
+            mbar_init(bar_acc_empty + 8u * i, CG * 4);     // one arrival per epilogue warp, of both CTAs for a pair
         }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -454,7 +453,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t a_hi = p.a_desc_hi, b_hi = p.b_desc_hi;
             const uint32_t a_ks = p.a_kstep, b_ks = p.b_kstep;
             const uint32_t idesc = p.idesc;
-            const uint32_t ready0 = FAST ? bar_full : bar_xform;
+            // A lone CTA in single-pass mode consumes the TMA barrier directly; otherwise the split warps
+            // (of both CTAs, for a pair) announce the stage on the leader's barrier.
+            const uint32_t ready0 = (FAST && CG == 1) ? bar_full : bar_xform;
             for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
                 const int iters = unit_iters(p, unit);
                 const int buf = acc_it & 1;
@@ -471,7 +472,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                     for (int ks = 0; ks < KSTEPS; ++ks) {
                         const uint32_t ak = a_lo + ks * a_ks, bk = b_lo + ks * b_ks;
-                        if constexpr (CG == 2) {
+                        if constexpr (CG == 2 && FAST) {
+                            if (elect_one()) umma_tf32_pair(d_tmem, ak, a_hi, bk, b_hi, idesc, accumulate);
+                        } else if constexpr (CG == 2) {
                             if (elect_one()) umma_tf32_pair(d_tmem, ak + LO16, a_hi, bk, b_hi, idesc, accumulate);
                             if (elect_one()) umma_tf32_pair(d_tmem, ak, a_hi, bk + LO16, b_hi, idesc, 1u);
                             if (elect_one()) umma_tf32_pair(d_tmem, ak, a_hi, bk, b_hi, idesc, 1u);
@@ -504,7 +507,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else if (warp < 2 + NS) {
         // ------------------------------------------------------------ hi/lo split
-        if (!FAST) {
+        // In single-pass mode there is nothing to split; for a CTA pair these warps still relay "my
+        // CTA's tile has landed" to the leader's barrier.
+        if (!FAST || CG == 2) {
             const int tid = threadIdx.x - 64;
             int stage = 0;
             uint32_t phase = 0;
@@ -514,7 +519,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             constexpr int NT = 32 * NS;                   // split threads
             constexpr int PER = N4 / NT;                  // float4s per thread
             constexpr int U = (PER % 4 == 0) ? 4 : (PER % 2 == 0 ? 2 : 1);
-            static_assert(N4 % NT == 0 && PER % U == 0, "stage size must divide over the split warps");
+            static_assert(FAST || (N4 % NT == 0 && PER % U == 0), "stage size must divide over the split warps");
             for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
                 const int iters = unit_iters(p, unit);
                 for (int it = 0; it < iters; ++it) {
@@ -523,7 +528,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const float4 *raw = reinterpret_cast<const float4 *>(stage_base + static_cast<size_t>(stage) * STAGE_BYTES);
                     float4 *lo = const_cast<float4 *>(raw) + N4;
 #pragma unroll
-                    for (int g = 0; g < PER; g += U) {
+                    for (int g = 0; g < (FAST ? 0 : PER); g += U) {
                         float4 v[U];
 #pragma unroll
                         for (int u = 0; u < U; ++u) v[u] = raw[tid + (g + u) * NT];
@@ -537,9 +542,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             lo[tid + (g + u) * NT] = l;
                         }
                     }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    if (CG == 2 && cta_rank != 0) mbar_arrive_cta(bar_xform + 8u * stage, 0u);
-                    else mbar_arrive(bar_xform + 8u * stage);
+                    // Every thread publishes its writes to the async proxy; one lane per warp then arrives
+                    // (a remote arrival crosses SMs, so they are kept to one per warp).
+                    if (!FAST) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (CG == 2 && cta_rank != 0) mbar_arrive_cta(bar_xform + 8u * stage, 0u);
+                        else mbar_arrive(bar_xform + 8u * stage);
+                    }
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -673,8 +683,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
             }
             tc_fence_before();
-            if (CG == 2 && cta_rank != 0) mbar_arrive_cta(bar_acc_empty + 8u * buf, 0u);
-            else mbar_arrive(bar_acc_empty + 8u * buf);
+            __syncwarp();
+            if (lane == 0) {
+                if (CG == 2 && cta_rank != 0) mbar_arrive_cta(bar_acc_empty + 8u * buf, 0u);
+                else mbar_arrive(bar_acc_empty + 8u * buf);
+            }
             ++acc_it;
         }
         if (use_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -857,7 +870,7 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     const int bn_env = env_int("MNI_B200_BN", 0);
     if (bn_env == 64 || bn_env == 128 || bn_env == 256) pl.bn = bn_env;
     // CTA pairs: 3xTF32 mode, 256-wide tiles, and at least two 128-row blocks of output.
-    pl.cg = (!p.fast_tf32 && pl.bn == 256 && p.M > BM && env_int("MNI_B200_CTA_PAIR", 1) != 0) ? 2 : 1;
+    pl.cg = (pl.bn == 256 && p.M > BM && env_int("MNI_B200_CTA_PAIR", 1) != 0) ? 2 : 1;
     pl.bk = (pl.bn == 256 && !p.fast_tf32) ? 16 : 32;
     const int bk_env = env_int("MNI_B200_BK", 0);
     if (bk_env == 16 || bk_env == 32) pl.bk = bk_env;
@@ -1067,8 +1080,10 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
         else if (split_warps == 8) e = launch_variant<BN_, BK_, false, 8, 1>(pl, tmA, tmB, tmC, tmD, k, stream); \
         else e = launch_variant<BN_, BK_, false, 4, 1>(pl, tmA, tmB, tmC, tmD, k, stream);                 \
     }
-    if (pl.cg == 2 && pl.bk == 16) e = launch_variant<256, 16, false, 8, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
-    if (pl.cg == 2 && pl.bk == 32) e = launch_variant<256, 32, false, 8, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
+    if (pl.cg == 2 && !p.fast_tf32 && pl.bk == 16) e = launch_variant<256, 16, false, 8, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
+    if (pl.cg == 2 && !p.fast_tf32 && pl.bk == 32) e = launch_variant<256, 32, false, 8, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
+    if (pl.cg == 2 && p.fast_tf32 && pl.bk == 16) e = launch_variant<256, 16, true, 4, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
+    if (pl.cg == 2 && p.fast_tf32 && pl.bk == 32) e = launch_variant<256, 32, true, 4, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
     MNI_VARIANT(64, 16) MNI_VARIANT(64, 32) MNI_VARIANT(128, 16) MNI_VARIANT(128, 32) MNI_VARIANT(256, 16)
     MNI_VARIANT(256, 32)
 #undef MNI_VARIANT
