@@ -6,10 +6,11 @@ the Linear bias add, as hand-written sm_100a kernels behind a C ABI.
 """
 from . import _lib  # noqa: F401
 from .ops import (  # noqa: F401
-    Linear, add, add_backward, bias_gelu, bias_gelu_backward, broadcast_shape, device_status, launch_count, matmul, matmul_backward,
-    matmul_bias_gelu, permute, permute_backward,
+    Linear, adamw_step, add, add_backward, bias_gelu, bias_gelu_backward, broadcast_shape, clip_and_step,
+    device_status, grad_norm, launch_count, matmul, matmul_backward, matmul_bias_gelu, permute, permute_backward,
+    softmax, softmax_backward,
 )
 from .tensor import DeviceTensor  # noqa: F401
 
-__all__ = ["DeviceTensor", "Linear", "add", "add_backward", "bias_gelu", "bias_gelu_backward", "broadcast_shape", "device_status",
-           "launch_count", "matmul", "matmul_backward", "matmul_bias_gelu", "permute", "permute_backward"]
+__all__ = ["DeviceTensor", "Linear", "adamw_step", "add", "add_backward", "bias_gelu", "bias_gelu_backward",
+           "broadcast_shape", "clip_and_step", "device_status", "grad_norm", "launch_count", "matmul", "matmul_backward", "matmul_bias_gelu", "permute", "permute_backward", "softmax", "softmax_backward"]

@@ -62,6 +62,13 @@ _SIGNATURES = {
     "mni_b200_bias_gelu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "mni_b200_bias_gelu_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                          C.c_int64, C.c_uint32, C.c_void_p]),
+    "mni_b200_softmax_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "mni_b200_softmax_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                       C.c_void_p]),
+    "mni_b200_grad_sumsq": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "mni_b200_adamw_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_float,
+                                      C.c_float, C.c_float, C.c_float, C.c_uint32, C.c_void_p, C.c_float, C.c_int,
+                                      C.c_void_p]),
     "mni_b200_contiguous": (C.c_int, [C.POINTER(View), C.c_void_p, C.c_void_p]),
     "mni_b200_workspace_set": (C.c_int, [C.c_void_p, C.c_size_t]),
     "mni_b200_workspace_query": (C.c_int, [C.POINTER(View), C.POINTER(View), C.c_uint32, C.POINTER(C.c_size_t)]),

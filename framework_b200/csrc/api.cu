@@ -660,6 +660,63 @@ int mni_b200_bias_gelu_bwd(const float *grad, const float *x, const float *bias,
     });
 }
 
+static int softmax_args(const void *p0, const void *p1, const void *p2, int64_t outer, int64_t dim, int64_t inner) {
+    if (outer < 0 || dim < 0 || inner < 0) return fail(MNI_B200_ERR_ARG, "negative extent");
+    if (outer == 0 || dim == 0 || inner == 0) return MNI_B200_OK;
+    if (!p0 || !p1 || !p2) return fail(MNI_B200_ERR_ARG, "null pointer");
+    if (outer > 0x7fffffffLL || inner > 0x7fffffffLL || dim > (INT64_MAX / outer) / inner ||
+        (inner > 1 && outer * inner / 32 >= 0x7fffffffLL))
+        return fail(MNI_B200_ERR_TOO_LARGE, "softmax extent too large");
+    return MNI_B200_OK;
+}
+
+int mni_b200_softmax_fwd(const float *x, float *out, int64_t outer, int64_t dim_size, int64_t inner, void *stream) {
+    int rc = softmax_args(x, out, out, outer, dim_size, inner);
+    if (rc || outer * dim_size * inner == 0) return rc;
+    DeviceState *st = nullptr;
+    rc = device_state(&st);
+    if (rc) return rc;
+    return launch_softmax_fwd(x, out, outer, dim_size, inner, static_cast<cudaStream_t>(stream));
+}
+
+int mni_b200_softmax_bwd(const float *grad, const float *out, float *dx, int64_t outer, int64_t dim_size,
+                         int64_t inner, void *stream) {
+    int rc = softmax_args(grad, out, dx, outer, dim_size, inner);
+    if (rc || outer * dim_size * inner == 0) return rc;
+    DeviceState *st = nullptr;
+    rc = device_state(&st);
+    if (rc) return rc;
+    return launch_softmax_bwd(grad, out, dx, outer, dim_size, inner, static_cast<cudaStream_t>(stream));
+}
+
+int mni_b200_grad_sumsq(const float *grad, int64_t n, double *sumsq, uint32_t flags, void *stream) {
+    if (n < 0) return fail(MNI_B200_ERR_ARG, "negative extent");
+    if (!sumsq) return fail(MNI_B200_ERR_ARG, "sumsq is null");
+    if (n > 0 && !grad) return fail(MNI_B200_ERR_ARG, "grad is null");
+    return with_scratch(flags, stream, [&](Call &c) -> int {
+        const size_t poff = c.arena.reserve(sumsq_partial_bytes(n, c.st->sm_count));
+        if (c.dry()) return MNI_B200_OK;
+        return launch_sumsq(grad, n, sumsq, (flags & MNI_B200_ACCUMULATE_C) != 0, c.at(poff), c.st->sm_count, c.stream);
+    });
+}
+
+int mni_b200_adamw_step(float *param, float *m, float *v, float *grad, int64_t n, float lr, float beta1, float beta2,
+                        float eps, float weight_decay, uint32_t step, const double *grad_sumsq, float max_grad_norm,
+                        int write_clipped_grad, void *stream) {
+    if (n < 0) return fail(MNI_B200_ERR_ARG, "negative extent");
+    if (n == 0) return MNI_B200_OK;
+    if (!param || !m || !v || !grad) return fail(MNI_B200_ERR_ARG, "null pointer");
+    if (step == 0) return fail(MNI_B200_ERR_ARG, "step counts from 1");
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    // bias corrections of ops/optimizer.rs:31-32: 1 - beta^step in f32
+    float p1 = 1.0f, p2 = 1.0f;
+    for (uint32_t i = 0; i < step; ++i) { p1 *= beta1; p2 *= beta2; }
+    return launch_adamw(param, m, v, grad, n, lr, beta1, beta2, eps, weight_decay, 1.0f - p1, 1.0f - p2, grad_sumsq,
+                        max_grad_norm, write_clipped_grad != 0, static_cast<cudaStream_t>(stream));
+}
+
 int mni_b200_contiguous(const mni_b200_view *src, float *dst, void *stream) {
     int rc = check_view(src, "src", 1);
     if (rc) return rc;

@@ -110,6 +110,15 @@ size_t colsum_partial_bytes(int64_t rows, int64_t n, int sm_count);
 int launch_colsum(const float *dy, int64_t ld, float *out, int64_t rows, int64_t n, bool accumulate,
                   float *partial, int sm_count, cudaStream_t stream);
 int launch_copy(const float *src, float *dst, int64_t n, cudaStream_t stream);
+int launch_adamw(float *param, float *m, float *v, float *grad, int64_t n, float lr, float beta1, float beta2,
+                 float eps, float weight_decay, float bc1, float bc2, const double *sumsq, float max_norm,
+                 bool write_grad, cudaStream_t stream);
+int launch_softmax_fwd(const float *x, float *out, int64_t outer, int64_t dim, int64_t inner, cudaStream_t stream);
+int launch_softmax_bwd(const float *dy, const float *out, float *dx, int64_t outer, int64_t dim, int64_t inner,
+                       cudaStream_t stream);
+size_t sumsq_partial_bytes(int64_t n, int sm_count);
+int launch_sumsq(const float *grad, int64_t n, double *out, bool accumulate, void *partial, int sm_count,
+                 cudaStream_t stream);
 // out = gelu_tanh(x + bias[col]);  dx = grad * gelu'(x + bias), dbias = column sums of dx (partial: colsum_partial_bytes)
 int launch_bias_gelu(const float *x, const float *bias, float *out, int64_t rows, int64_t n, cudaStream_t stream);
 int launch_bias_gelu_bwd(const float *grad, const float *x, const float *bias, float *dx, float *dbias,

@@ -172,6 +172,106 @@ __global__ void bias_gelu_bwd_partial_kernel(const float *__restrict__ grad, con
     }
 }
 
+// ---- AdamW step: the consumer of the weight gradient (kernels/adamw.cu) -------------------------
+// One pass: grad read once, m / v / param read and written once (28 bytes per element).
+__device__ __forceinline__ void adamw_one(float &p, float &m, float &v, float g, float lr, float beta1, float beta2,
+                                          float eps, float decay, float bc1, float bc2) {
+    const float mi = beta1 * m + (1.0f - beta1) * g;
+    const float vi = beta2 * v + (1.0f - beta2) * g * g;
+    m = mi;
+    v = vi;
+    p = p * decay - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+}
+// Clip factor of ops/optimizer.rs:232-236: max_norm / norm when the norm (f64 sum of squares, rounded to
+// f32, then sqrt) exceeds max_norm, else 1.  The sum of squares is read from device memory, so no
+// host round trip sits between the norm and the step.
+__device__ __forceinline__ float clip_scale(const double *sumsq, float max_norm) {
+    if (sumsq == nullptr || !(max_norm > 0.0f)) return 1.0f;
+    const float norm = sqrtf(static_cast<float>(*sumsq));
+    return norm > max_norm ? max_norm / norm : 1.0f;
+}
+__global__ void adamw_vec_kernel(float4 *__restrict__ param, float4 *__restrict__ m, float4 *__restrict__ v,
+                                 float4 *__restrict__ grad, long long n4, float lr, float beta1, float beta2,
+                                 float eps, float decay, float bc1, float bc2, const double *sumsq, float max_norm,
+                                 int write_grad) {
+    const float scale = clip_scale(sumsq, max_norm);
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float4 p = param[i], mm = m[i], vv = v[i];
+        float4 g = __ldcs(grad + i);
+        if (scale != 1.0f) {
+            g.x *= scale; g.y *= scale; g.z *= scale; g.w *= scale;
+            if (write_grad) grad[i] = g;
+        }
+        adamw_one(p.x, mm.x, vv.x, g.x, lr, beta1, beta2, eps, decay, bc1, bc2);
+        adamw_one(p.y, mm.y, vv.y, g.y, lr, beta1, beta2, eps, decay, bc1, bc2);
+        adamw_one(p.z, mm.z, vv.z, g.z, lr, beta1, beta2, eps, decay, bc1, bc2);
+        adamw_one(p.w, mm.w, vv.w, g.w, lr, beta1, beta2, eps, decay, bc1, bc2);
+        param[i] = p; m[i] = mm; v[i] = vv;
+    }
+}
+__global__ void adamw_scalar_kernel(float *__restrict__ param, float *__restrict__ m, float *__restrict__ v,
+                                    float *__restrict__ grad, long long n, float lr, float beta1, float beta2,
+                                    float eps, float decay, float bc1, float bc2, const double *sumsq, float max_norm,
+                                    int write_grad) {
+    const float scale = clip_scale(sumsq, max_norm);
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float g = grad[i];
+        if (scale != 1.0f) {
+            g *= scale;
+            if (write_grad) grad[i] = g;
+        }
+        adamw_one(param[i], m[i], v[i], g, lr, beta1, beta2, eps, decay, bc1, bc2);
+    }
+}
+
+// ---- gradient norm (ops/optimizer.rs:126-138): f64 sum of f32 squares ------------------------------
+// Stage 1: a fixed grid, each thread a grid-stride f64 sum, each block a fixed-order tree -> partial[block].
+// Stage 2: one block adds the partials in a fixed order.  The grid depends only on n and the SM count,
+// so the result is reproducible run to run.
+constexpr int kNormThreads = 256;
+__device__ __forceinline__ double block_sum_f64(double x) {
+    __shared__ double warp_sums[kNormThreads / 32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = x;
+    __syncthreads();
+    double t = 0.0;
+    if (threadIdx.x == 0)
+        for (int w = 0; w < kNormThreads / 32; ++w) t += warp_sums[w];
+    return t;   // valid in thread 0
+}
+__global__ void __launch_bounds__(kNormThreads)
+sumsq_partial_kernel(const float *__restrict__ g, long long n, double *__restrict__ partial) {
+    double acc = 0.0;
+    const long long tid = blockIdx.x * static_cast<long long>(kNormThreads) + threadIdx.x;
+    const long long nthreads = static_cast<long long>(gridDim.x) * kNormThreads;
+    if ((reinterpret_cast<uintptr_t>(g) & 15) == 0) {
+        const long long n4 = n / 4;
+        const float4 *g4 = reinterpret_cast<const float4 *>(g);
+        for (long long i = tid; i < n4; i += nthreads) {
+            const float4 t = __ldg(g4 + i);
+            acc += static_cast<double>(t.x) * t.x;
+            acc += static_cast<double>(t.y) * t.y;
+            acc += static_cast<double>(t.z) * t.z;
+            acc += static_cast<double>(t.w) * t.w;
+        }
+        for (long long i = n4 * 4 + tid; i < n; i += nthreads) acc += static_cast<double>(g[i]) * g[i];
+    } else {
+        for (long long i = tid; i < n; i += nthreads) acc += static_cast<double>(g[i]) * g[i];
+    }
+    const double t = block_sum_f64(acc);
+    if (threadIdx.x == 0) partial[blockIdx.x] = t;
+}
+__global__ void __launch_bounds__(kNormThreads)
+sumsq_final_kernel(const double *__restrict__ partial, int count, double *__restrict__ out, int accumulate) {
+    double acc = 0.0;
+    for (int i = threadIdx.x; i < count; i += kNormThreads) acc += partial[i];
+    const double t = block_sum_f64(acc);
+    if (threadIdx.x == 0) *out = accumulate ? *out + t : t;
+}
+
 struct PackArgs {
     int nd;
     long long shape[kMaxDims];
@@ -307,6 +407,41 @@ int launch_bias_gelu_bwd(const float *grad, const float *x, const float *bias, f
     colsum_final_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(partial, dbias, n, slabs,
                                                                                   accumulate ? 1 : 0);
     MNI_LAUNCH_CHECK("colsum_final_kernel");
+    return MNI_B200_OK;
+}
+
+int launch_adamw(float *param, float *m, float *v, float *grad, int64_t n, float lr, float beta1, float beta2,
+                 float eps, float weight_decay, float bc1, float bc2, const double *sumsq, float max_norm,
+                 bool write_grad, cudaStream_t stream) {
+    if (n == 0) return MNI_B200_OK;
+    const float decay = 1.0f - lr * weight_decay;
+    const bool vec = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(param) | reinterpret_cast<uintptr_t>(m) |
+                                       reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(grad)) & 15) == 0;
+    if (vec)
+        adamw_vec_kernel<<<grid_for(n / 4, 256), 256, 0, stream>>>(
+            reinterpret_cast<float4 *>(param), reinterpret_cast<float4 *>(m), reinterpret_cast<float4 *>(v),
+            reinterpret_cast<float4 *>(grad), n / 4, lr, beta1, beta2, eps, decay, bc1, bc2, sumsq, max_norm,
+            write_grad ? 1 : 0);
+    else
+        adamw_scalar_kernel<<<grid_for(n, 256), 256, 0, stream>>>(param, m, v, grad, n, lr, beta1, beta2, eps, decay, bc1,
+                                                                 bc2, sumsq, max_norm, write_grad ? 1 : 0);
+    MNI_LAUNCH_CHECK("adamw");
+    return MNI_B200_OK;
+}
+
+int sumsq_blocks(int64_t n, int sm_count) {
+    const int64_t want = (n + 4 * kNormThreads - 1) / (4 * kNormThreads);
+    return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, 4 * static_cast<int64_t>(sm_count))));
+}
+size_t sumsq_partial_bytes(int64_t n, int sm_count) { return sizeof(double) * sumsq_blocks(n, sm_count); }
+int launch_sumsq(const float *grad, int64_t n, double *out, bool accumulate, void *partial, int sm_count,
+                 cudaStream_t stream) {
+    const int blocks = sumsq_blocks(n, sm_count);
+    double *p = static_cast<double *>(partial);
+    sumsq_partial_kernel<<<blocks, kNormThreads, 0, stream>>>(grad, n, p);
+    MNI_LAUNCH_CHECK("sumsq_partial");
+    sumsq_final_kernel<<<1, kNormThreads, 0, stream>>>(p, blocks, out, accumulate ? 1 : 0);
+    MNI_LAUNCH_CHECK("sumsq_final");
     return MNI_B200_OK;
 }
 

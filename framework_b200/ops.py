@@ -147,6 +147,87 @@ def matmul_bias_gelu(a: DeviceTensor, b: DeviceTensor, bias: DeviceTensor, *, fl
     return pre, out
 
 
+def _softmax_split(shape: Sequence[int], dim: int) -> Tuple[int, int, int]:
+    d = dim + len(shape) if dim < 0 else dim
+    if not 0 <= d < len(shape):
+        raise IndexError(f"softmax dim {dim} out of range for shape {tuple(shape)}")
+    return max(shape_size(shape[:d]), 1) if d else 1, shape[d], max(shape_size(shape[d + 1:]), 1)
+
+
+def softmax(a: DeviceTensor, dim: int = -1) -> DeviceTensor:
+    """``ops::norm::softmax`` (ops/norm.rs:52-89).  A strided input is gathered first, as the reference's
+    ``dev_ptr`` read assumes row-major data."""
+    a = a if a.is_contiguous() else a.contiguous()
+    outer, size, inner = _softmax_split(a.shape, dim)
+    out = DeviceTensor.empty(a.shape, a.storage.device)
+    _lib.check(_lib.lib().mni_b200_softmax_fwd(a.ptr, out.ptr, outer, size, inner, current_stream()))
+    return out
+
+
+def softmax_backward(grad: DeviceTensor, out: DeviceTensor, dim: int = -1) -> DeviceTensor:
+    """``ops::norm::softmax_backward`` (ops/norm.rs:125-163) from the saved forward output."""
+    if tuple(grad.shape) != tuple(out.shape):
+        raise ValueError("grad and out must have the same shape")
+    grad = grad if grad.is_contiguous() else grad.contiguous()
+    out = out if out.is_contiguous() else out.contiguous()
+    outer, size, inner = _softmax_split(out.shape, dim)
+    dx = DeviceTensor.empty(out.shape, out.storage.device)
+    _lib.check(_lib.lib().mni_b200_softmax_bwd(grad.ptr, out.ptr, dx.ptr, outer, size, inner, current_stream()))
+    return dx
+
+
+def _grad_sumsq(grads: Sequence[DeviceTensor]) -> "torch.Tensor":
+    """Squared global gradient norm as a one-element f64 device tensor (no host read)."""
+    import torch
+    sumsq = torch.empty(1, dtype=torch.float64, device=grads[0].storage.device)
+    for i, g in enumerate(grads):
+        if not g.is_contiguous():
+            raise ValueError("gradients must be contiguous")
+        flags = _lib.ACCUMULATE_C if i else 0
+        _lib.check(_lib.lib().mni_b200_grad_sumsq(g.ptr, g.size, sumsq.data_ptr(), flags, current_stream()))
+    return sumsq
+
+
+def grad_norm(grads: Sequence[DeviceTensor]) -> float:
+    """``ops::optimizer::grad_norm`` (ops/optimizer.rs:126-171): sqrt of the f64 sum of squares, as f32."""
+    if not grads:
+        return 0.0
+    import numpy as np
+    return float(np.sqrt(np.float32(_grad_sumsq(grads).item())))
+
+
+def adamw_step(param: DeviceTensor, m: DeviceTensor, v: DeviceTensor, grad: DeviceTensor, *, lr: float,
+               beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.0,
+               step: int = 1, grad_sumsq=None, max_grad_norm: float = 0.0, write_clipped_grad: bool = True) -> None:
+    """``ops::optimizer::adamw_step`` for one parameter (ops/optimizer.rs:67-120): in-place update.
+    ``grad_sumsq`` (a one-element f64 device tensor) with ``max_grad_norm`` > 0 applies the clip of
+    ``clip_and_step`` inside the same pass."""
+    if not (param.is_contiguous() and m.is_contiguous() and v.is_contiguous() and grad.is_contiguous()):
+        raise ValueError("adamw_step needs contiguous tensors")
+    if not (param.size == m.size == v.size == grad.size):
+        raise ValueError("param, m, v and grad must have the same size")
+    sq = grad_sumsq.data_ptr() if grad_sumsq is not None else None
+    _lib.check(_lib.lib().mni_b200_adamw_step(param.ptr, m.ptr, v.ptr, grad.ptr, param.size, lr, beta1, beta2, eps,
+                                              weight_decay, int(step), sq, max_grad_norm,
+                                              1 if write_clipped_grad else 0, current_stream()))
+
+
+def clip_and_step(params: Sequence[DeviceTensor], ms: Sequence[DeviceTensor], vs: Sequence[DeviceTensor],
+                  grads: Sequence[DeviceTensor], *, lr: float, beta1: float = 0.9, beta2: float = 0.999,
+                  eps: float = 1e-8, weight_decay: float = 0.0, step: int = 1, max_grad_norm: float = 0.0) -> float:
+    """``ops::optimizer::clip_and_step`` (ops/optimizer.rs:247-276): global-norm clip and AdamW over all
+    parameters; returns the norm before clipping.  The norm stays on the device until every step kernel is
+    queued; the read that returns it is the call's only synchronisation."""
+    if not params:
+        return 0.0
+    import numpy as np
+    sumsq = _grad_sumsq(grads)
+    for p, m, v, g in zip(params, ms, vs, grads):
+        adamw_step(p, m, v, g, lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, step=step,
+                   grad_sumsq=sumsq, max_grad_norm=max_grad_norm)
+    return float(np.sqrt(np.float32(sumsq.item())))
+
+
 def permute(a: DeviceTensor, dims: Sequence[int]) -> DeviceTensor:
     """``ops::layout::permute``: a stride-only view sharing the storage (what the reference's CPU backend
     does, ops/layout.rs:112-134); the matmul kernels read it in place."""

@@ -156,6 +156,39 @@ MNI_B200_API int mni_b200_bias_gelu_bwd(const float *grad, const float *x, const
                                         float *dbias, int64_t rows, int64_t n, uint32_t flags, void *stream);
 
 /*
+ * Softmax over one dimension of a contiguous tensor seen as [outer, dim_size, inner], and its backward
+ * from the saved output.  Replace the softmax_forward_f32 / softmax_backward_f32 launches of
+ * ops/norm.rs:52-89 and :125-163 (kernels/softmax.cu); arithmetic as the CPU backend (ops/norm.rs:10-50,
+ * :95-123): subtract the maximum, exp, divide by the sum; dx = out * (grad - sum(grad * out)).
+ */
+MNI_B200_API int mni_b200_softmax_fwd(const float *x, float *out, int64_t outer, int64_t dim_size, int64_t inner,
+                                      void *stream);
+MNI_B200_API int mni_b200_softmax_bwd(const float *grad, const float *out, float *dx, int64_t outer,
+                                      int64_t dim_size, int64_t inner, void *stream);
+
+/*
+ * Sum of squares of one gradient in f64, into a device double: the per-parameter term of grad_norm
+ * (ops/optimizer.rs:126-171, kernel grad_norm_sq_partial_f32).  With MNI_B200_ACCUMULATE_C the term
+ * is added to *sumsq, so a loop over the parameters leaves the squared global norm on the device and
+ * no host read sits between the norm and the step.  Fixed grid and summation order: reproducible.
+ */
+MNI_B200_API int mni_b200_grad_sumsq(const float *grad, int64_t n, double *sumsq, uint32_t flags, void *stream);
+
+/*
+ * AdamW step on one parameter, the consumer of the weight gradient.  Replaces the adamw_step_f32 launch
+ * of ops/optimizer.rs:67-120 (kernels/adamw.cu): m, v and param are updated in place from grad in one
+ * pass; `step` counts from 1 and sets the bias corrections 1 - beta^step.  m and v start as zeros.
+ * With grad_sumsq non-null and max_grad_norm > 0 this is clip_and_step (ops/optimizer.rs:247-276):
+ * norm = sqrt((float)*grad_sumsq); when norm > max_grad_norm every gradient element is multiplied by
+ * max_grad_norm / norm before use, and written back to grad when write_clipped_grad is non-zero (the
+ * reference's grad_clip_f32 pass leaves the gradients scaled).
+ */
+MNI_B200_API int mni_b200_adamw_step(float *param, float *m, float *v, float *grad, int64_t n, float lr, float beta1,
+                                     float beta2, float eps, float weight_decay, uint32_t step,
+                                     const double *grad_sumsq, float max_grad_norm, int write_clipped_grad,
+                                     void *stream);
+
+/*
  * Same result as mni_b200_add_bias_bwd, for callers that must never see this library
  * allocate device memory: a runtime that owns the device's memory budget through its own
  * allocator, or a step loop that cannot take the device-wide stall of cudaMalloc/cudaFree.

@@ -335,6 +335,82 @@ void oracle_bias_gelu_bwd(const float *grad, const float *x, const float *bias, 
     }
 }
 
+/* ops/norm.rs:10-50  softmax over dimension d of a row-major tensor seen as [outer, dim, inner]. */
+void oracle_softmax(const float *a, float *out, int64_t outer, int64_t dim, int64_t inner) {
+    for (int64_t o = 0; o < outer; ++o)
+        for (int64_t i = 0; i < inner; ++i) {
+            float max_val = -INFINITY;
+            for (int64_t s = 0; s < dim; ++s) max_val = fmaxf(max_val, a[o * dim * inner + s * inner + i]);
+            float sum = 0.0f;
+            for (int64_t s = 0; s < dim; ++s) {
+                const int64_t idx = o * dim * inner + s * inner + i;
+                const float e = expf(a[idx] - max_val);
+                out[idx] = e;
+                sum += e;
+            }
+            for (int64_t s = 0; s < dim; ++s) out[o * dim * inner + s * inner + i] /= sum;
+        }
+}
+
+/* ops/norm.rs:95-123  softmax backward from the saved output: dot = sum(grad * sm); out = sm * (grad - dot). */
+void oracle_softmax_bwd(const float *grad, const float *sm, float *out, int64_t outer, int64_t dim, int64_t inner) {
+    for (int64_t o = 0; o < outer; ++o)
+        for (int64_t i = 0; i < inner; ++i) {
+            float dot = 0.0f;
+            for (int64_t s = 0; s < dim; ++s) {
+                const int64_t idx = o * dim * inner + s * inner + i;
+                dot += grad[idx] * sm[idx];
+            }
+            for (int64_t s = 0; s < dim; ++s) {
+                const int64_t idx = o * dim * inner + s * inner + i;
+                out[idx] = sm[idx] * (grad[idx] - dot);
+            }
+        }
+}
+
+/* ops/optimizer.rs:22-65  AdamW on one parameter, CPU backend: decoupled decay first (only if
+ * weight_decay > 0), then the moment updates and the bias-corrected step.  bc = 1 - beta^step. */
+void oracle_adamw_step(float *data, float *m, float *v, const float *grad, int64_t n, float lr, float beta1,
+                       float beta2, float eps, float weight_decay, int step) {
+    float p1 = 1.0f, p2 = 1.0f;
+    for (int i = 0; i < step; ++i) { p1 *= beta1; p2 *= beta2; }
+    const float bc1 = 1.0f - p1, bc2 = 1.0f - p2;
+    for (int64_t i = 0; i < n; ++i) {
+        const float g = grad[i];
+        if (weight_decay > 0.0f) data[i] *= 1.0f - lr * weight_decay;
+        m[i] = beta1 * m[i] + (1.0f - beta1) * g;
+        v[i] = beta2 * v[i] + (1.0f - beta2) * g * g;
+        const float m_hat = m[i] / bc1;
+        const float v_hat = v[i] / bc2;
+        data[i] -= lr * m_hat / (sqrtf(v_hat) + eps);
+    }
+}
+
+/* ops/optimizer.rs:126-138  global gradient norm: f64 sum of squares over the gradients in order,
+ * rounded to f32, then sqrt. */
+float oracle_grad_norm(const float *const *grads, const int64_t *sizes, int count) {
+    double norm_sq = 0.0;
+    for (int p = 0; p < count; ++p)
+        for (int64_t i = 0; i < sizes[p]; ++i) norm_sq += (double)grads[p][i] * (double)grads[p][i];
+    return sqrtf((float)norm_sq);
+}
+
+/* ops/optimizer.rs:226-245  clip_and_step, CPU backend: norm, in-place scaling of every gradient when
+ * max_grad_norm > 0 and norm > max_grad_norm, then AdamW on each parameter; returns the norm. */
+float oracle_clip_and_step(float *const *params, float *const *ms, float *const *vs, float *const *grads,
+                           const int64_t *sizes, int count, float lr, float beta1, float beta2, float eps,
+                           float weight_decay, int step, float max_grad_norm) {
+    const float norm = oracle_grad_norm((const float *const *)grads, sizes, count);
+    if (max_grad_norm > 0.0f && norm > max_grad_norm) {
+        const float scale = max_grad_norm / norm;
+        for (int p = 0; p < count; ++p)
+            for (int64_t i = 0; i < sizes[p]; ++i) grads[p][i] *= scale;
+    }
+    for (int p = 0; p < count; ++p)
+        oracle_adamw_step(params[p], ms[p], vs[p], grads[p], sizes[p], lr, beta1, beta2, eps, weight_decay, step);
+    return norm;
+}
+
 int oracle_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

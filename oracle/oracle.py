@@ -203,6 +203,62 @@ def bias_gelu_backward(grad: HostTensor, x: HostTensor, bias: HostTensor):
     return HostTensor(dx, tuple(x.shape), _row_major(x.shape)), HostTensor(db, (x.shape[-1],), (1,))
 
 
+def adamw_step(data: np.ndarray, m: np.ndarray, v: np.ndarray, grad: np.ndarray, *, lr, beta1=0.9, beta2=0.999,
+               eps=1e-8, weight_decay=0.0, step=1) -> None:
+    """ops/optimizer.rs:22-65 (CPU backend), in place on flat f32 arrays."""
+    lib().oracle_adamw_step(_fp(data), _fp(m), _fp(v), _fp(grad), C.c_int64(data.size), C.c_float(lr),
+                            C.c_float(beta1), C.c_float(beta2), C.c_float(eps), C.c_float(weight_decay), C.c_int(step))
+
+
+def _split(shape, dim):
+    d = dim + len(shape) if dim < 0 else dim
+    outer = int(np.prod(shape[:d], dtype=np.int64)) if d else 1
+    inner = int(np.prod(shape[d + 1:], dtype=np.int64)) if d + 1 < len(shape) else 1
+    return max(outer, 1), int(shape[d]), max(inner, 1)
+
+
+def softmax(a: np.ndarray, dim: int = -1) -> np.ndarray:
+    """ops/norm.rs:10-50 on a C-contiguous f32 array."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    out = np.empty_like(a)
+    outer, size, inner = _split(a.shape, dim)
+    lib().oracle_softmax(_fp(a), _fp(out), C.c_int64(outer), C.c_int64(size), C.c_int64(inner))
+    return out
+
+
+def softmax_backward(grad: np.ndarray, sm: np.ndarray, dim: int = -1) -> np.ndarray:
+    """ops/norm.rs:95-123."""
+    grad = np.ascontiguousarray(grad, dtype=np.float32)
+    sm = np.ascontiguousarray(sm, dtype=np.float32)
+    out = np.empty_like(sm)
+    outer, size, inner = _split(sm.shape, dim)
+    lib().oracle_softmax_bwd(_fp(grad), _fp(sm), _fp(out), C.c_int64(outer), C.c_int64(size), C.c_int64(inner))
+    return out
+
+
+def _ptr_array(arrays):
+    return (_f32p * len(arrays))(*[_fp(a) for a in arrays])
+
+
+def grad_norm(grads) -> float:
+    """ops/optimizer.rs:126-138 over a list of flat f32 arrays."""
+    fn = lib().oracle_grad_norm
+    fn.restype = C.c_float
+    sizes = (C.c_int64 * len(grads))(*[g.size for g in grads])
+    return float(fn(_ptr_array(grads), sizes, C.c_int(len(grads))))
+
+
+def clip_and_step(params, ms, vs, grads, *, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1,
+                  max_grad_norm=0.0) -> float:
+    """ops/optimizer.rs:226-245 (CPU backend), in place on lists of flat f32 arrays; returns the norm."""
+    fn = lib().oracle_clip_and_step
+    fn.restype = C.c_float
+    sizes = (C.c_int64 * len(params))(*[p.size for p in params])
+    return float(fn(_ptr_array(params), _ptr_array(ms), _ptr_array(vs), _ptr_array(grads), sizes,
+                    C.c_int(len(params)), C.c_float(lr), C.c_float(beta1), C.c_float(beta2), C.c_float(eps),
+                    C.c_float(weight_decay), C.c_int(step), C.c_float(max_grad_norm)))
+
+
 def matmul_contig_raw(a: np.ndarray, b: np.ndarray, out: np.ndarray, batch: int, a_batch: int,
                       b_batch: int, m: int, k: int, n: int, threads: int) -> None:
     """The bare loop nest of ops/matmul.rs:54-70 on caller-owned buffers (bench baseline)."""

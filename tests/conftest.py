@@ -27,6 +27,17 @@ def oracle():
     return O
 
 
+@pytest.fixture(scope="session")
+def F():
+    """The package with its CUDA library loaded; a GPU test without a device fails, it does not skip."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    import framework_b200 as pkg
+    pkg._lib.lib()
+    return pkg
+
+
 def tol_3xtf32(k, a, b):
     """Acceptance bound of the default precision mode: 1e-5 * K * max|a| * max|b|."""
     ma = float(np.max(np.abs(a))) if np.size(a) else 0.0

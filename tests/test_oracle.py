@@ -152,3 +152,54 @@ def test_error_cases(oracle):
     with pytest.raises(ValueError, match="broadcastable"):
         O.matmul(O.HostTensor.from_array(np.zeros((2, 2, 3), np.float32)),
                  O.HostTensor.from_array(np.zeros((3, 3, 2), np.float32)))
+
+
+def test_adamw_first_step_moves_by_lr_times_sign(oracle):
+    """ops/optimizer.rs:22-65: with zero moments, step 1 gives m_hat = g and v_hat = g*g, so every weight moves
+    by lr * g / (|g| + eps) after the decoupled decay; checked against float64 arithmetic of the same formula."""
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal(1001).astype(np.float32)
+    g = rng.standard_normal(1001).astype(np.float32)
+    m, v = np.zeros_like(w), np.zeros_like(w)
+    w0 = w.copy()
+    oracle.adamw_step(w, m, v, g, lr=1e-2, weight_decay=0.1, step=1)
+    g64 = g.astype(np.float64)
+    want = w0.astype(np.float64) * (1 - 1e-2 * 0.1) - 1e-2 * g64 / (np.abs(g64) + 1e-8)
+    assert np.max(np.abs(w - want)) < 1e-6
+    assert np.allclose(m, 0.1 * g, rtol=1e-6) and np.allclose(v, 0.001 * g * g, rtol=1e-4)  # 1 - 0.999f is 0.00100005
+    # a second step with zero gradient only decays the moments
+    oracle.adamw_step(w, m, v, np.zeros_like(g), lr=0.0, step=2)
+    assert np.allclose(m, 0.09 * g, rtol=1e-6)
+
+
+def test_clip_and_step_scales_the_gradients_in_place(oracle):
+    """ops/optimizer.rs:226-245: the norm is returned unclipped, the gradients are left scaled to max_grad_norm."""
+    g = [np.full(4, 3.0, np.float32), np.full(9, 4.0, np.float32)]       # norm = sqrt(36 + 144)
+    p = [np.ones(4, np.float32), np.ones(9, np.float32)]
+    m = [np.zeros(4, np.float32), np.zeros(9, np.float32)]
+    v = [np.zeros(4, np.float32), np.zeros(9, np.float32)]
+    assert abs(oracle.grad_norm(g) - np.sqrt(180.0)) < 1e-5
+    norm = oracle.clip_and_step(p, m, v, g, lr=0.1, step=1, max_grad_norm=1.0)
+    assert abs(norm - np.sqrt(180.0)) < 1e-5
+    assert abs(oracle.grad_norm(g) - 1.0) < 1e-6
+    assert np.allclose(p[0], 0.9, atol=1e-6) and np.allclose(p[1], 0.9, atol=1e-6)   # lr * sign(g)
+
+
+def test_softmax_reference_checks(oracle):
+    """The reference's own softmax checks (test/nn.test.ts:47-54): input [[1,2,3],[1,2,3]], dim 1 — rows sum to 1
+    within 1e-4, all positive, ordering preserved; plus the closed form and the backward's zero row sums."""
+    x = np.array([[1, 2, 3], [1, 2, 3]], np.float32)
+    sm = oracle.softmax(x, 1)
+    assert abs(sm[0].sum() - 1.0) < 1e-4 and abs(sm[1].sum() - 1.0) < 1e-4
+    assert (sm > 0).all() and sm[0, 2] > sm[0, 1] > sm[0, 0]
+    want = np.exp(x.astype(np.float64) - 3.0)
+    want /= want.sum(axis=1, keepdims=True)
+    assert np.max(np.abs(sm - want)) < 1e-7
+    # over dim 0 both entries of a column are equal
+    assert np.allclose(oracle.softmax(x, 0), 0.5)
+    g = np.array([[0.5, -1.0, 2.0], [1.0, 1.0, 1.0]], np.float32)
+    dx = oracle.softmax_backward(g, sm, 1)
+    assert np.max(np.abs(dx.sum(axis=1))) < 1e-6          # softmax gradients sum to zero along the dim
+    assert np.max(np.abs(dx[1])) < 1e-7                   # a constant upstream gradient gives zero
+    j = np.diag(want[0]) - np.outer(want[0], want[0])     # Jacobian of softmax
+    assert np.max(np.abs(dx[0] - j @ g[0].astype(np.float64))) < 1e-6
