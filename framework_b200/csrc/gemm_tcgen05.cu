@@ -39,6 +39,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int kMaxStages = 8;
+constexpr int kEpiWarps = 8;                                // two per TMEM lane quarter, half of the columns each
 constexpr int kEpiBufBytes = 32 * 128;                     // one 32 x 32 f32 patch
 constexpr int kBarBytes = (3 * kMaxStages + 4) * 8 + 16;
 constexpr long long kWaitCycles = 4000000000LL;            // ~2 s at 2 GHz
@@ -306,7 +307,7 @@ __device__ __forceinline__ void load_operand(int mode, uint32_t dst, const CUten
 // 256 x BN tile with cta_group::2 MMAs issued by the pair's leader; each CTA stages its own 128 rows
 // of A and half (BN/2 rows) of B, so shared-memory and L2 traffic per flop drop by a third.
 template <int BN, int BK, bool FAST, int NS, int CG>
-__global__ void __launch_bounds__(32 * (6 + NS), 1)
+__global__ void __launch_bounds__(32 * (2 + NS + kEpiWarps), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
                const KParams p) {
@@ -325,7 +326,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                                 ~static_cast<uintptr_t>(1023));
     uint8_t *stage_base = smem;
     uint8_t *epi_base = smem + static_cast<size_t>(p.stages) * STAGE_BYTES;      // 1024-aligned
-    uint64_t *bars = reinterpret_cast<uint64_t *>(epi_base + 4 * p.epi_patches * kEpiBufBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(epi_base + kEpiWarps * p.epi_patches * kEpiBufBytes);
     // bars: full[S] | xform[S] | empty[S] | acc_full[2] | acc_empty[2]
     const uint32_t bar_full = smem_u32(bars);
     const uint32_t bar_xform = bar_full + 8u * kMaxStages;
@@ -350,7 +351,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_acc_full + 8u * i, 1);
-            mbar_init(bar_acc_empty + 8u * i, CG * 4);     // one arrival per epilogue warp, of both CTAs for a pair
+            mbar_init(bar_acc_empty + 8u * i, CG * kEpiWarps);   // one arrival per epilogue warp, of both CTAs for a pair
         }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -517,9 +518,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             long long waited = 0;
             constexpr int N4 = RAW_BYTES >> 4;            // float4 count of the raw stage
             constexpr int NT = 32 * NS;                   // split threads
-            constexpr int PER = N4 / NT;                  // float4s per thread
-            constexpr int U = (PER % 4 == 0) ? 4 : (PER % 2 == 0 ? 2 : 1);
-            static_assert(FAST || (N4 % NT == 0 && PER % U == 0), "stage size must divide over the split warps");
+            constexpr int PER = (N4 + NT - 1) / NT;       // float4s per thread (the last round may be partial)
+            constexpr bool EXACT = N4 % NT == 0;
+            constexpr int U = !EXACT ? 1 : (PER % 4 == 0) ? 4 : (PER % 2 == 0 ? 2 : 1);
             for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
                 const int iters = unit_iters(p, unit);
                 for (int it = 0; it < iters; ++it) {
@@ -531,9 +532,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     for (int g = 0; g < (FAST ? 0 : PER); g += U) {
                         float4 v[U];
 #pragma unroll
-                        for (int u = 0; u < U; ++u) v[u] = raw[tid + (g + u) * NT];
+                        for (int u = 0; u < U; ++u)
+                            if (EXACT || tid + (g + u) * NT < N4) v[u] = raw[tid + (g + u) * NT];
 #pragma unroll
                         for (int u = 0; u < U; ++u) {
+                            if (!EXACT && tid + (g + u) * NT >= N4) continue;
                             float4 l;
                             l.x = v[u].x - __uint_as_float(__float_as_uint(v[u].x) & 0xFFFFE000u);
                             l.y = v[u].y - __uint_as_float(__float_as_uint(v[u].y) & 0xFFFFE000u);
@@ -558,7 +561,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else {
         // ------------------------------------------------------------ epilogue
         const int q = warp & 3;                       // TMEM lane quarter this warp may read
-        uint8_t *my_stage = epi_base + (warp - (2 + NS)) * p.epi_patches * kEpiBufBytes;
+        const int ew = warp - (2 + NS);               // 0..7: warps ew and ew+4 share a lane quarter ...
+        constexpr int CHUNKS = BN / 32 / (kEpiWarps / 4);   // ... and take half of the tile's 32-column chunks each
+        const int chunk_lo = (ew >> 2) * CHUNKS;
+        uint8_t *my_stage = epi_base + ew * p.epi_patches * kEpiBufBytes;
         int acc_it = 0;
         int patch = 0;                                // staging buffer to use next
         int in_flight = 0;                            // bulk groups committed by lane 0 and not yet waited for
@@ -579,27 +585,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int cbatch = fuse ? t.bt : t.split * p.batch + t.bt;
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
             if (row0 < p.M) {
-                for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                for (int chunk = chunk_lo; chunk < chunk_lo + CHUNKS; ++chunk) {
                     const int col0 = t.tn * BN + chunk * 32;
                     if (col0 >= p.N) break;           // warp-uniform
                     uint32_t v[32];
                     __syncwarp();                      // tcgen05.ld is warp-collective
-                    const long long t_ld0 = clock64();
+                    const long long t_ld0 = p.prof ? clock64() : 0;
                     tmem_ld32_issue(tbase + chunk * 32, v);
                     tmem_ld_wait();
-                    t_ld += clock64() - t_ld0;
+                    if (p.prof) t_ld += clock64() - t_ld0;
                     // Stages the 32 values of this lane's row into the warp's next patch and hands the
                     // patch to the TMA unit (store, or reduce-add for C += ...).
                     auto emit = [&](const CUtensorMap *map, bool reduce) {
-                        const long long t_wg0 = clock64();
+                        const long long t_wg0 = p.prof ? clock64() : 0;
                         if (lane == 0 && in_flight == p.epi_patches) {   // the patch must have been read by its store
-                            if (p.epi_patches == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                            if (p.epi_patches == 1) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                            else if (p.epi_patches == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                             else if (p.epi_patches == 4) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
                             else asm volatile("cp.async.bulk.wait_group.read 7;" ::: "memory");
                             --in_flight;
                         }
                         __syncwarp();
-                        t_wg += clock64() - t_wg0;
+                        if (p.prof) t_wg += clock64() - t_wg0;
                         uint8_t *dst = my_stage + patch * kEpiBufBytes + lane * 128;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
@@ -717,25 +724,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
 }
 
-// Deterministic split-K finish: C = sum_s partial[s] (+ bias) (+ C).
-__global__ void splitk_reduce_kernel(const float *__restrict__ partial, float *__restrict__ C, long long ldc,
-                                     long long c_bstride, const float *__restrict__ bias, int accumulate,
-                                     int splits, long long batch, int M, int N) {
-    const long long total = batch * M * N;
-    const long long slab = total;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int col = static_cast<int>(i % N);
-        const long long r = i / N;
-        const int row = static_cast<int>(r % M);
-        const long long bt = r / M;
-        float acc = partial[i];
-        for (int s = 1; s < splits; ++s) acc += partial[s * slab + i];
-        if (bias) acc += __ldg(bias + col);
-        float *dst = C + bt * c_bstride + static_cast<long long>(row) * ldc + col;
-        if (accumulate) acc += *dst;
-        *dst = acc;
+// Deterministic split-K finish: C = sum_s partial[s] (+ bias) (+ C), splits added in ascending order.
+// One thread per vector of the output (two divisions per thread, none per element); the partials of
+// four splits are in flight at a time.
+template <typename V, typename I>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float *__restrict__ partial, float *__restrict__ C, long long ldc, long long c_bstride,
+                     const float *__restrict__ bias, int accumulate, int splits, long long rows, int M, int N) {
+    constexpr int W = sizeof(V) / sizeof(float);
+    const I per_row = static_cast<I>(N / W);
+    const I item = static_cast<I>(blockIdx.x) * 256 + threadIdx.x;
+    if (item >= static_cast<I>(rows) * per_row) return;
+    const I row = item / per_row;
+    const int col = static_cast<int>(item - row * per_row) * W;
+    const I bt = row / static_cast<I>(M);
+    const int m = static_cast<int>(row - bt * static_cast<I>(M));
+    const long long slab = rows * N;
+    const float *src = partial + static_cast<long long>(row) * N + col;
+    float acc[W];
+#pragma unroll
+    for (int e = 0; e < W; ++e) acc[e] = 0.f;
+    int sp = 0;
+    for (; sp + 4 <= splits; sp += 4) {
+        V t[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) t[u] = __ldcg(reinterpret_cast<const V *>(src + (sp + u) * slab));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float *tv = reinterpret_cast<const float *>(&t[u]);
+#pragma unroll
+            for (int e = 0; e < W; ++e) acc[e] += tv[e];
+        }
     }
+    for (; sp < splits; ++sp) {
+        const V t = __ldcg(reinterpret_cast<const V *>(src + sp * slab));
+        const float *tv = reinterpret_cast<const float *>(&t);
+#pragma unroll
+        for (int e = 0; e < W; ++e) acc[e] += tv[e];
+    }
+    if (bias) {
+        const V b = __ldg(reinterpret_cast<const V *>(bias + col));
+        const float *bv = reinterpret_cast<const float *>(&b);
+#pragma unroll
+        for (int e = 0; e < W; ++e) acc[e] += bv[e];
+    }
+    V *out = reinterpret_cast<V *>(C + static_cast<long long>(bt) * c_bstride + static_cast<long long>(m) * ldc + col);
+    if (accumulate) {
+        const V c0 = *out;
+        const float *cv = reinterpret_cast<const float *>(&c0);
+#pragma unroll
+        for (int e = 0; e < W; ++e) acc[e] += cv[e];
+    }
+    *out = *reinterpret_cast<const V *>(acc);
 }
 
 // ------------------------------------------------------------------ host side
@@ -870,7 +910,8 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     const int bn_env = env_int("MNI_B200_BN", 0);
     if (bn_env == 64 || bn_env == 128 || bn_env == 256) pl.bn = bn_env;
     // CTA pairs: 3xTF32 mode, 256-wide tiles, and at least two 128-row blocks of output.
-    pl.cg = (pl.bn == 256 && p.M > BM && env_int("MNI_B200_CTA_PAIR", 1) != 0) ? 2 : 1;
+    const int pair_env = env_int("MNI_B200_CTA_PAIR", 1);     // 0 never, 1 for 256-wide tiles, 2 for every width
+    pl.cg = (p.M > BM && (pair_env >= 2 || (pair_env == 1 && pl.bn == 256))) ? 2 : 1;
     pl.bk = (pl.bn == 256 && !p.fast_tf32) ? 16 : 32;
     const int bk_env = env_int("MNI_B200_BK", 0);
     if (bk_env == 16 || bk_env == 32) pl.bk = bk_env;
@@ -880,14 +921,14 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     // Tiles with a short contraction spend their time in the epilogue: give it more TMA stores in
     // flight (staging patches) and the main loop fewer stages.  Long contractions get the deepest pipeline.
     const long long iters_per_tile = p.fold * ((p.K + pl.bk - 1) / pl.bk);
-    pl.patches = 2;   // measured: more patches (fewer stages) never helped
+    pl.patches = 1;   // staging patches per epilogue warp
     (void)iters_per_tile;
     const int pt_env = env_int("MNI_B200_EPI_PATCHES", 0);
-    if (pt_env == 2 || pt_env == 4 || pt_env == 8) pl.patches = pt_env;
-    size_t fixed = kFixedSmemNoEpi + static_cast<size_t>(4 * pl.patches) * kEpiBufBytes;
+    if (pt_env == 1 || pt_env == 2 || pt_env == 4) pl.patches = pt_env;
+    size_t fixed = kFixedSmemNoEpi + static_cast<size_t>(kEpiWarps * pl.patches) * kEpiBufBytes;
     while (pl.patches > 2 && (budget - fixed) / stage < 2) {
         pl.patches /= 2;
-        fixed = kFixedSmemNoEpi + static_cast<size_t>(4 * pl.patches) * kEpiBufBytes;
+        fixed = kFixedSmemNoEpi + static_cast<size_t>(kEpiWarps * pl.patches) * kEpiBufBytes;
     }
     pl.stages = static_cast<int>(std::min<size_t>(kMaxStages, (budget - fixed) / stage));
     const int st_env = env_int("MNI_B200_STAGES", 0);
@@ -930,7 +971,7 @@ cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtenso
     if (attr != cudaSuccess) return attr;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(pl.grid));
-    cfg.blockDim = dim3(32 * (6 + NS));
+    cfg.blockDim = dim3(32 * (2 + NS + kEpiWarps));
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[1];
@@ -1080,20 +1121,35 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
         else if (split_warps == 8) e = launch_variant<BN_, BK_, false, 8, 1>(pl, tmA, tmB, tmC, tmD, k, stream); \
         else e = launch_variant<BN_, BK_, false, 4, 1>(pl, tmA, tmB, tmC, tmD, k, stream);                 \
     }
-    if (pl.cg == 2 && !p.fast_tf32 && pl.bk == 16) e = launch_variant<256, 16, false, 8, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
-    if (pl.cg == 2 && !p.fast_tf32 && pl.bk == 32) e = launch_variant<256, 32, false, 8, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
-    if (pl.cg == 2 && p.fast_tf32 && pl.bk == 16) e = launch_variant<256, 16, true, 4, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
-    if (pl.cg == 2 && p.fast_tf32 && pl.bk == 32) e = launch_variant<256, 32, true, 4, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
+#define MNI_PAIR_VARIANT(BN_, BK_)                                                                    \
+    if (pl.cg == 2 && pl.bn == BN_ && pl.bk == BK_) {                                                 \
+        if (p.fast_tf32) e = launch_variant<BN_, BK_, true, 4, 2>(pl, tmA, tmB, tmC, tmD, k, stream);      \
+        else e = launch_variant<BN_, BK_, false, 8, 2>(pl, tmA, tmB, tmC, tmD, k, stream);                 \
+    }
+    MNI_PAIR_VARIANT(64, 16) MNI_PAIR_VARIANT(64, 32) MNI_PAIR_VARIANT(128, 16) MNI_PAIR_VARIANT(128, 32)
+    MNI_PAIR_VARIANT(256, 16) MNI_PAIR_VARIANT(256, 32)
+#undef MNI_PAIR_VARIANT
     MNI_VARIANT(64, 16) MNI_VARIANT(64, 32) MNI_VARIANT(128, 16) MNI_VARIANT(128, 32) MNI_VARIANT(256, 16)
     MNI_VARIANT(256, 32)
 #undef MNI_VARIANT
     if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "gemm_tc_kernel set-up failed: %s", cudaGetErrorString(e));
     MNI_LAUNCH_CHECK("gemm_tc_kernel");
     if (pl.splits > 1) {
-        const long long total = static_cast<long long>(p.batch) * p.M * p.N;
-        const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 8));
-        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partial, p.C, p.ldc, p.c_bstride, p.bias, p.accumulate,
-                                                         pl.splits, p.batch, k.M, k.N);
+        const long long rows = static_cast<long long>(p.batch) * p.M;
+        const bool vec = p.N % 4 == 0 && p.ldc % 4 == 0 && p.c_bstride % 4 == 0 &&
+                         ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(partial) |
+                           reinterpret_cast<uintptr_t>(p.bias)) & 15) == 0;
+        const long long items = rows * (vec ? p.N / 4 : p.N);
+        const unsigned blocks = static_cast<unsigned>((items + 255) / 256);
+        const bool small = items < (1LL << 31) - 256;
+#define MNI_REDUCE(V_, I_)                                                                                          \
+    splitk_reduce_kernel<V_, I_><<<blocks, 256, 0, stream>>>(partial, p.C, p.ldc, p.c_bstride, p.bias, p.accumulate, \
+                                                             pl.splits, rows, k.M, k.N)
+        if (vec && small) MNI_REDUCE(float4, unsigned);
+        else if (vec) MNI_REDUCE(float4, long long);
+        else if (small) MNI_REDUCE(float, unsigned);
+        else MNI_REDUCE(float, long long);
+#undef MNI_REDUCE
         MNI_LAUNCH_CHECK("splitk_reduce_kernel");
     }
     return MNI_B200_OK;
