@@ -101,18 +101,22 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 // Bounded wait.  Returns false if the CTA is aborting (this waiter or another gave up).
-// `waited` accumulates the cycles spent blocked (role-level wait accounting).
+// With `timed`, `waited` accumulates the cycles spent blocked (role-level wait accounting, including
+// the time the first try_wait is suspended by the hardware); without it the satisfied case costs one
+// try_wait and no clock reads.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          unsigned int *err, uint32_t code, long long &waited) {
-    const long long t0 = clock64();
+                                          unsigned int *err, uint32_t code, long long &waited, bool timed) {
+    long long t0 = 0;
+    if (timed) t0 = clock64();
     if (mbar_try_wait(bar, parity)) {
-        waited += clock64() - t0;
+        if (timed) waited += clock64() - t0;
         return true;
     }
+    if (!timed) t0 = clock64();
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) {
-            waited += clock64() - t0;
+            if (timed) waited += clock64() - t0;
             return true;
         }
         if ((++spins & 63u) == 0u) {
@@ -127,9 +131,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 // Warp-collective form: every lane polls, the verdict is made uniform.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                               unsigned int *err, uint32_t code, long long &waited) {
-    const bool ok = mbar_wait(bar, parity, abort_flag, err, code, waited);
+                                               unsigned int *err, uint32_t code, long long &waited, bool timed) {
+    const bool ok = mbar_wait(bar, parity, abort_flag, err, code, waited, timed);
     return __all_sync(0xffffffffu, ok);
+}
+// Non-blocking look at a barrier phase (try_wait may suspend the thread; this never does).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
 }
 // True in exactly one lane of a converged warp.  The TMA and MMA issuing warps run their loops
 // warp-uniformly and predicate only the issuing instruction with this: descriptors and
@@ -174,6 +190,28 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint32_t a_lo, uint32
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}"
         ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// A operand from tensor memory (lanes = rows, one 32-bit column per k element), B from shared memory.
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -306,7 +344,11 @@ __device__ __forceinline__ void load_operand(int mode, uint32_t dst, const CUten
 // CG = 1: one CTA computes a 128 x BN tile.  CG = 2: a pair of CTAs (a 2-CTA cluster) computes a
 // 256 x BN tile with cta_group::2 MMAs issued by the pair's leader; each CTA stages its own 128 rows
 // of A and half (BN/2 rows) of B, so shared-memory and L2 traffic per flop drop by a third.
-template <int BN, int BK, bool FAST, int NS, int CG>
+// TA = true (3xTF32, lone CTA, BK = 32, BN <= 128): the A operand of the MMAs comes from tensor memory.
+// The split warps read each landed A row once, and store hi and lo with tcgen05.st into a TMEM slot
+// of the stage (columns 2*BN + stage*64: 32 of hi, 32 of lo); no lo copy of A is written to shared
+// memory and no MMA re-reads A from it, which is what bounds narrow tiles otherwise.
+template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false>
 __global__ void __launch_bounds__(32 * (2 + NS + kEpiWarps), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
@@ -315,11 +357,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr uint32_t A_BYTES = BM * BK * 4;
     constexpr uint32_t B_BYTES = BNL * BK * 4;
     constexpr uint32_t RAW_BYTES = A_BYTES + B_BYTES;
-    constexpr uint32_t STAGE_BYTES = FAST ? RAW_BYTES : 2 * RAW_BYTES;
+    static_assert(!TA || (!FAST && CG == 1 && BK == 32 && NS == 8 && BN <= 128), "unsupported A-from-TMEM variant");
+    constexpr uint32_t STAGE_BYTES = FAST ? RAW_BYTES : (TA ? A_BYTES + 2 * B_BYTES : 2 * RAW_BYTES);
     constexpr uint32_t STAGE16 = STAGE_BYTES >> 4;
-    constexpr uint32_t LO16 = RAW_BYTES >> 4;              // lo copy of the stage, 16-byte units
+    constexpr uint32_t LO16 = (TA ? B_BYTES : RAW_BYTES) >> 4;   // lo copy relative to its raw tile, 16-byte units
     constexpr int KSTEPS = BK / 8;
-    constexpr uint32_t TMEM_COLS = 2 * BN;                 // 128 / 256 / 512: double-buffered accumulator
+    constexpr uint32_t TMEM_COLS = TA ? 512 : 2 * BN;      // double-buffered accumulator (+ the A slots)
+    constexpr uint32_t TA_COL0 = 2 * BN;                   // first column of the A slots
+    constexpr uint32_t TA_SLOT = 2 * BK;                   // hi | lo
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -338,6 +383,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const bool timed = p.prof != nullptr;
     const long long t_kernel0 = clock64();
     const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;   // 0 = the pair's leader
     const int unit0 = static_cast<int>(blockIdx.x) / CG;           // this CTA (pair) starts at this unit ...
@@ -405,7 +451,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const int rowA = t.tm * (BM * CG) + static_cast<int>(cta_rank) * BM;
                 const int rowB = t.tn * BN + static_cast<int>(cta_rank) * BNL;
                 for (int it = t.it0; it < t.it1; ++it) {
-                    ok = mbar_wait_warp(bar_empty + 8u * stage, phase ^ 1u, abort_flag, p.err, 0x100u | stage, waited);
+                    ok = mbar_wait_warp(bar_empty + 8u * stage, phase ^ 1u, abort_flag, p.err, 0x100u | stage, waited, timed);
                     if (!ok) break;
                     const uint32_t full = bar_full + 8u * stage;
                     const int k0 = kk * BK;
@@ -447,6 +493,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int acc_it = 0;
             bool ok = true;
             long long waited = 0, waited_acc = 0;
+            bool next_ready = false;                   // the stage about to be consumed was already seen complete
             const uint32_t sa0 = smem_u32(stage_base);
             const uint32_t a_lo0 = ((sa0 >> 4) & 0x3FFFu) | p.a_desc_lbo;
             const uint32_t b_lo0 = (((sa0 + A_BYTES) >> 4) & 0x3FFFu) | p.b_desc_lbo;
@@ -461,19 +508,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const int iters = unit_iters(p, unit);
                 const int buf = acc_it & 1;
                 const uint32_t acc_phase = (acc_it >> 1) & 1;
-                ok = mbar_wait_warp(bar_acc_empty + 8u * buf, acc_phase ^ 1u, abort_flag, p.err, 0x200u | buf, waited_acc);
+                ok = mbar_wait_warp(bar_acc_empty + 8u * buf, acc_phase ^ 1u, abort_flag, p.err, 0x200u | buf, waited_acc, timed);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
                 uint32_t accumulate = 0;
                 for (int it = 0; it < iters; ++it) {
-                    ok = mbar_wait_warp(ready0 + 8u * stage, phase, abort_flag, p.err, 0x300u | stage, waited);
-                    if (!ok) break;
+                    if (!next_ready) {
+                        ok = mbar_wait_warp(ready0 + 8u * stage, phase, abort_flag, p.err, 0x300u | stage, waited, timed);
+                        if (!ok) break;
+                    }
                     tc_fence_after();
+                    // Look at the following stage now; the answer is used after this stage's MMAs are
+                    // queued, so the barrier read overlaps them (narrow tiles retire an MMA every 32
+                    // cycles and would otherwise drain the queue during the wait).
+                    const int nstage = stage + 1 == p.stages ? 0 : stage + 1;
+                    const uint32_t peek = mbar_test_wait(ready0 + 8u * nstage, stage + 1 == p.stages ? phase ^ 1u : phase);
 #pragma unroll
                     for (int ks = 0; ks < KSTEPS; ++ks) {
                         const uint32_t ak = a_lo + ks * a_ks, bk = b_lo + ks * b_ks;
-                        if constexpr (CG == 2 && FAST) {
+                        if constexpr (TA) {
+                            const uint32_t at = tmem_base + TA_COL0 + static_cast<uint32_t>(stage) * TA_SLOT + ks * 8;
+                            if (elect_one()) umma_tf32_ts(d_tmem, at + BK, bk, b_hi, idesc, accumulate);
+                            if (elect_one()) umma_tf32_ts(d_tmem, at, bk + LO16, b_hi, idesc, 1u);
+                            if (elect_one()) umma_tf32_ts(d_tmem, at, bk, b_hi, idesc, 1u);
+                        } else if constexpr (CG == 2 && FAST) {
                             if (elect_one()) umma_tf32_pair(d_tmem, ak, a_hi, bk, b_hi, idesc, accumulate);
                         } else if constexpr (CG == 2) {
                             if (elect_one()) umma_tf32_pair(d_tmem, ak + LO16, a_hi, bk, b_hi, idesc, accumulate);
@@ -490,6 +549,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     if constexpr (CG == 2) { if (elect_one()) umma_commit_pair(bar_empty + 8u * stage); }
                     else { if (elect_one()) umma_commit(bar_empty + 8u * stage); }
+                    next_ready = __all_sync(0xffffffffu, peek != 0u);
                     if (++stage == p.stages) {
                         stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0;
                     } else {
@@ -516,7 +576,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t phase = 0;
             bool ok = true;
             long long waited = 0;
-            constexpr int N4 = RAW_BYTES >> 4;            // float4 count of the raw stage
+            constexpr int N4 = (TA ? B_BYTES : RAW_BYTES) >> 4;   // float4 count of what gets a lo copy
             constexpr int NT = 32 * NS;                   // split threads
             constexpr int PER = (N4 + NT - 1) / NT;       // float4s per thread (the last round may be partial)
             constexpr bool EXACT = N4 % NT == 0;
@@ -524,9 +584,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
                 const int iters = unit_iters(p, unit);
                 for (int it = 0; it < iters; ++it) {
-                    ok = mbar_wait(bar_full + 8u * stage, phase, abort_flag, p.err, 0x400u | stage, waited);
+                    ok = mbar_wait(bar_full + 8u * stage, phase, abort_flag, p.err, 0x400u | stage, waited, timed);
                     if (!ok) break;
-                    const float4 *raw = reinterpret_cast<const float4 *>(stage_base + static_cast<size_t>(stage) * STAGE_BYTES);
+                    if constexpr (TA) {
+                        // A: this thread owns row (lane quarter of its warp) and 16 of the 32 k columns.
+                        const uint8_t *sa = stage_base + static_cast<size_t>(stage) * STAGE_BYTES;
+                        const int half = (warp - 2) >> 2;
+                        const int row = (warp & 3) * 32 + lane;
+                        uint32_t hi[16], lo16[16];
+                        if (p.a_mode == kKMajor) {
+                            // 128-byte rows, 16-byte chunk c of row r sits at chunk c ^ (r % 8)
+                            const uint8_t *rp = sa + row * 128;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float4 x = *reinterpret_cast<const float4 *>(rp + (((half * 4 + j) ^ (row & 7)) << 4));
+                                hi[4 * j + 0] = __float_as_uint(x.x); hi[4 * j + 1] = __float_as_uint(x.y);
+                                hi[4 * j + 2] = __float_as_uint(x.z); hi[4 * j + 3] = __float_as_uint(x.w);
+                            }
+                        } else {
+                            // 32-row chunks of BK k-lines of 128 bytes; 32-byte atom a of k-line k sits at a ^ (k % 4)
+                            const uint8_t *cp = sa + (row >> 5) * (128 * BK) + ((row & 7) << 2);
+                            const int atom = (row & 31) >> 3;
+#pragma unroll
+                            for (int kk = 0; kk < 16; ++kk) {
+                                const int k = half * 16 + kk;
+                                hi[kk] = *reinterpret_cast<const uint32_t *>(cp + k * 128 + ((atom ^ (k & 3)) << 5));
+                            }
+                        }
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const float x = __uint_as_float(hi[e]);
+                            hi[e] &= 0xFFFFE000u;
+                            lo16[e] = __float_as_uint(x - __uint_as_float(hi[e]));
+                        }
+                        const uint32_t ta = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + TA_COL0 +
+                                            static_cast<uint32_t>(stage) * TA_SLOT + half * 16;
+                        __syncwarp();                      // tcgen05.st is warp-collective
+                        tmem_st16(ta, hi);
+                        tmem_st16(ta + BK, lo16);
+                        tmem_st_wait();
+                        tc_fence_before();
+                    }
+                    // TA: only the B tile gets a lo copy in shared memory (it sits right behind the raw B tile).
+                    const float4 *raw = reinterpret_cast<const float4 *>(stage_base + static_cast<size_t>(stage) * STAGE_BYTES +
+                                                                         (TA ? A_BYTES : 0));
                     float4 *lo = const_cast<float4 *>(raw) + N4;
 #pragma unroll
                     for (int g = 0; g < (FAST ? 0 : PER); g += U) {
@@ -576,7 +677,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const TileCoord t = decode_unit(p, unit);
             const int buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
-            ok = mbar_wait(bar_acc_full + 8u * buf, acc_phase, abort_flag, p.err, 0x500u | buf, waited);
+            ok = mbar_wait(bar_acc_full + 8u * buf, acc_phase, abort_flag, p.err, 0x500u | buf, waited, timed);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -899,6 +1000,7 @@ int make_output_map(CUtensorMap *map, float *ptr, int64_t N, int64_t M, int64_t 
 struct Plan {
     int bn, bk, cg, stages, splits, tiles_m, tiles_n, grid;   // cg = CTAs per tile (1, or 2 = CTA pair)
     int patches;                                              // epilogue staging patches per warp
+    bool ta;                                                  // A operand of the MMAs from tensor memory
     size_t smem;
 };
 
@@ -915,8 +1017,12 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     pl.bk = (pl.bn == 256 && !p.fast_tf32) ? 16 : 32;
     const int bk_env = env_int("MNI_B200_BK", 0);
     if (bk_env == 16 || bk_env == 32) pl.bk = bk_env;
+    // Narrow tiles of a lone CTA are bound by shared-memory bandwidth; taking A from tensor memory removes
+    // most of A's share of it.
+    pl.ta = !p.fast_tf32 && pl.cg == 1 && pl.bk == 32 && pl.bn <= 128 && env_int("MNI_B200_SPLIT_WARPS", 8) == 8 &&
+            env_int("MNI_B200_TMEM_A", 1) != 0;
     const size_t raw = static_cast<size_t>(BM + pl.bn / pl.cg) * pl.bk * 4;
-    const size_t stage = p.fast_tf32 ? raw : 2 * raw;
+    const size_t stage = p.fast_tf32 ? raw : (pl.ta ? raw + static_cast<size_t>(pl.bn) * pl.bk * 4 : 2 * raw);
     const size_t budget = 227 * 1024;
     // Tiles with a short contraction spend their time in the epilogue: give it more TMA stores in
     // flight (staging patches) and the main loop fewer stages.  Long contractions get the deepest pipeline.
@@ -931,6 +1037,7 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
         fixed = kFixedSmemNoEpi + static_cast<size_t>(kEpiWarps * pl.patches) * kEpiBufBytes;
     }
     pl.stages = static_cast<int>(std::min<size_t>(kMaxStages, (budget - fixed) / stage));
+    if (pl.ta) pl.stages = std::min(pl.stages, (512 - 2 * pl.bn) / (2 * pl.bk));   // one TMEM slot per stage
     const int st_env = env_int("MNI_B200_STAGES", 0);
     if (st_env >= 1 && st_env <= pl.stages) pl.stages = st_env;
     pl.smem = fixed + static_cast<size_t>(pl.stages) * stage;
@@ -959,13 +1066,13 @@ uint32_t desc_hi_bits(uint32_t sbo_bytes, uint32_t layout_type) {
     return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (layout_type << 29);
 }
 
-template <int BN, int BK, bool FAST, int NS, int CG>
+template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false>
 cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
                            const CUtensorMap &tmD, const KParams &k, cudaStream_t stream) {
     static std::once_flag once;
     static cudaError_t attr = cudaSuccess;
     std::call_once(once, [] {
-        attr = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FAST, NS, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        attr = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FAST, NS, CG, TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024);
     });
     if (attr != cudaSuccess) return attr;
@@ -981,7 +1088,7 @@ cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtenso
     attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = CG == 2 ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK, FAST, NS, CG>, tmA, tmB, tmC, tmD, k);
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK, FAST, NS, CG, TA>, tmA, tmB, tmC, tmD, k);
 }
 
 }  // namespace
@@ -1090,7 +1197,7 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     k.b_d2 = static_cast<int>(p.B.bshape[2]);
     k.stages = pl.stages;
     k.epi_patches = pl.patches;
-    k.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.A.k_major ? 0u : 1u) << 15) |
+    k.idesc = (1u << 4) | (2u << 7) | (2u << 10) | (((p.A.k_major || pl.ta) ? 0u : 1u) << 15) |
               ((p.B.k_major ? 0u : 1u) << 16) | (static_cast<uint32_t>(pl.bn >> 3) << 17) |
               (static_cast<uint32_t>((BM * pl.cg) >> 4) << 24);
     // K-major tile: rows of BK floats, 8-row groups SBO apart, swizzle span = one row.
@@ -1115,8 +1222,10 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
 
     cudaError_t e = cudaErrorInvalidValue;
     const int split_warps = env_int("MNI_B200_SPLIT_WARPS", 8);
+    if (pl.ta && pl.bn == 64) e = launch_variant<64, 32, false, 8, 1, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+    if (pl.ta && pl.bn == 128) e = launch_variant<128, 32, false, 8, 1, true>(pl, tmA, tmB, tmC, tmD, k, stream);
 #define MNI_VARIANT(BN_, BK_)                                                                         \
-    if (pl.cg == 1 && pl.bn == BN_ && pl.bk == BK_) {                                                 \
+    if (pl.cg == 1 && !pl.ta && pl.bn == BN_ && pl.bk == BK_) {                                                 \
         if (p.fast_tf32) e = launch_variant<BN_, BK_, true, 4, 1>(pl, tmA, tmB, tmC, tmD, k, stream);      \
         else if (split_warps == 8) e = launch_variant<BN_, BK_, false, 8, 1>(pl, tmA, tmB, tmC, tmD, k, stream); \
         else e = launch_variant<BN_, BK_, false, 4, 1>(pl, tmA, tmB, tmC, tmD, k, stream);                 \
