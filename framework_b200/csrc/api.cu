@@ -5,6 +5,7 @@
 
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -33,10 +34,19 @@ struct DeviceState {
     uint8_t *user_ws = nullptr;   // caller-provided scratch (takes precedence)
     size_t user_bytes = 0;
     unsigned int *err_word = nullptr;
+    // Second stream of small backward calls: dA and dB of a small problem each occupy a fraction of
+    // the GPU, so they are issued side by side (fork / join through events; also under stream capture).
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 DeviceState g_dev[kMaxDevices];
 
 int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+bool env_flag(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return (v && *v ? atoi(v) : dflt) != 0;
+}
 
 // Bump allocator over the device's scratch.  In dry mode nothing is touched: the
 // same host logic runs and only the byte count is produced (workspace_query).
@@ -74,6 +84,10 @@ int device_state(DeviceState **out) {
         st.err_word = static_cast<unsigned int *>(p);
         e = cudaMemset(st.err_word, 0, sizeof(unsigned int));
         if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "cudaMemset: %s", cudaGetErrorString(e));
+        e = cudaStreamCreateWithFlags(&st.side, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&st.ev_fork, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&st.ev_join, cudaEventDisableTiming);
+        if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "side stream set-up: %s", cudaGetErrorString(e));
         st.init = true;
     }
     *out = &st;
@@ -466,6 +480,26 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
         }
     }
 
+    // A small problem's two gradient products each fill only part of the GPU (and a skinny one's are short,
+    // launch-bound kernels): issue grad_b on the side stream next to grad_a and join before returning.
+    const double work = static_cast<double>(s.M) * static_cast<double>(s.N) * static_cast<double>(s.K) *
+                        static_cast<double>(std::max<int64_t>(g_batch, 1));
+    const bool overlap = !c.dry() && da && db && a_elems > 0 && b_elems > 0 && work > 0 && work <= 768.0 * 768.0 * 768.0 &&
+                         env_flag("MNI_B200_BWD_OVERLAP", 1);
+    cudaStream_t const main_stream = c.stream;
+    if (overlap) {
+        MNI_CUDA(cudaEventRecord(c.st->ev_fork, main_stream));
+        MNI_CUDA(cudaStreamWaitEvent(c.st->side, c.st->ev_fork, 0));
+    }
+    struct Join {      // joins the side stream on every exit path once it has been forked
+        Call &c; cudaStream_t main; bool on;
+        ~Join() {
+            if (!on) return;
+            c.stream = main;
+            if (cudaEventRecord(c.st->ev_join, c.st->side) == cudaSuccess) cudaStreamWaitEvent(main, c.st->ev_join, 0);
+        }
+    } join{c, main_stream, overlap};
+
     // grad_a = unbroadcast(dc . b^T, a.shape)   (ops/matmul.rs:231-240)
     if (da && a_elems > 0) {
         if (s.N == 0 || g_batch == 0) {
@@ -501,6 +535,7 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
     }
 
     // grad_b = unbroadcast(a^T . dc, b.shape)   (ops/matmul.rs:242-251)
+    if (overlap) c.stream = c.st->side;
     if (db && b_elems > 0) {
         if (s.M == 0 || g_batch == 0) {
             rc = zero_or_bias_fill(c, db, b_elems, 1, nullptr, acc_db);

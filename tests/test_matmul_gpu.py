@@ -347,3 +347,33 @@ def test_linearity_at_full_size_config2(F):
     assert float((y12 - y1 - y2).abs().max()) <= 3 * bound
     ref = (x1.double() @ w.double())
     assert float((y1.double() - ref).abs().max()) <= 1e-5 * 1024 * 1.0 * float(w.abs().max())
+
+
+def test_small_backward_side_stream_inside_a_cuda_graph(F, oracle):
+    """A small backward issues grad_b on the library's side stream (fork/join through events).  Captured into a
+    CUDA graph and replayed twice with new inputs, both gradients must still match the oracle."""
+    import torch
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((96, 80), dtype=np.float32)
+    b = rng.standard_normal((80, 72), dtype=np.float32)
+    g = rng.standard_normal((96, 72), dtype=np.float32)
+    ad, bd, gd = (F.DeviceTensor.from_numpy(x) for x in (a, b, g))
+    da, db = F.DeviceTensor.empty(a.shape), F.DeviceTensor.empty(b.shape)
+    F.matmul_backward(gd, ad, bd, da=da, db=db)            # eager once: scratch is sized before capture
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            F.matmul_backward(gd, ad, bd, da=da, db=db)
+    for seed in (1, 2):
+        g2 = np.random.default_rng(seed).standard_normal(g.shape, dtype=np.float32)
+        gd.storage.copy_(torch.from_numpy(g2.ravel()))
+        da.storage.zero_(); db.storage.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        H = oracle.HostTensor
+        ra, rb = oracle.matmul_backward(H.from_array(g2), H.from_array(a), H.from_array(b))
+        assert np.max(np.abs(da.numpy() - ra.numpy())) <= tol_3xtf32(72, g2, b)
+        assert np.max(np.abs(db.numpy() - rb.numpy())) <= tol_3xtf32(96, a, g2)
+    F.device_status()
