@@ -43,6 +43,12 @@ DeviceState g_dev[kMaxDevices];
 
 int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
+// Largest M*N*K*batch for which the two gradient products of a backward call are issued side by side.
+double overlap_work_limit() {
+    const char *v = getenv("MNI_B200_BWD_OVERLAP_WORK");
+    return v && *v ? atof(v) : 4.0e9;   // measured: helps up to the attention-shaped products (1.6e9), neutral beyond
+}
+
 bool env_flag(const char *name, int dflt) {
     const char *v = getenv(name);
     return (v && *v ? atoi(v) : dflt) != 0;
@@ -480,11 +486,12 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
         }
     }
 
-    // A small problem's two gradient products each fill only part of the GPU (and a skinny one's are short,
-    // launch-bound kernels): issue grad_b on the side stream next to grad_a and join before returning.
+    // The two gradient products of a small problem each fill only part of the GPU, a skinny one's are short,
+    // launch-bound kernels, and a medium one's leave a ragged last wave: issue grad_b on the side stream next
+    // to grad_a and join before returning.
     const double work = static_cast<double>(s.M) * static_cast<double>(s.N) * static_cast<double>(s.K) *
                         static_cast<double>(std::max<int64_t>(g_batch, 1));
-    const bool overlap = !c.dry() && da && db && a_elems > 0 && b_elems > 0 && work > 0 && work <= 768.0 * 768.0 * 768.0 &&
+    const bool overlap = !c.dry() && da && db && a_elems > 0 && b_elems > 0 && work > 0 && work <= overlap_work_limit() &&
                          env_flag("MNI_B200_BWD_OVERLAP", 1);
     cudaStream_t const main_stream = c.stream;
     if (overlap) {
