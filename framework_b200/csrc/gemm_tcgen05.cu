@@ -1011,9 +1011,35 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     pl.bn = p.N <= 64 ? 64 : (p.N <= 128 ? 128 : 256);
     const int bn_env = env_int("MNI_B200_BN", 0);
     if (bn_env == 64 || bn_env == 128 || bn_env == 256) pl.bn = bn_env;
-    // CTA pairs: 3xTF32 mode, 256-wide tiles, and at least two 128-row blocks of output.
+    // CTA pairs: 256-wide tiles and at least two 128-row blocks of output.
     const int pair_env = env_int("MNI_B200_CTA_PAIR", 1);     // 0 never, 1 for 256-wide tiles, 2 for every width
-    pl.cg = (p.M > BM && (pair_env >= 2 || (pair_env == 1 && pl.bn == 256))) ? 2 : 1;
+    auto pair_for = [&](int bn) { return (p.M > BM && (pair_env >= 2 || (pair_env == 1 && bn == 256))) ? 2 : 1; };
+    // Problems with fewer 128 x 256 tiles than SMs are latency-bound: one tile's k-loop is a serial
+    // TMA -> split -> MMA chain, so narrower tiles and a K split put more SMs on it.  The tile width and the
+    // split are chosen by a small cost model fitted to measured times of 256^3 .. 1024^3 products:
+    // nanoseconds per k element of one tile (30 / 33 for a 256-wide pair / lone CTA, 15.4 for 128, 13.5
+    // for 64), 1.5 us for the reduce launch and its traffic at 3 TB/s.
+    int model_splits = 0;
+    const long long tiles256 = static_cast<long long>(p.batch) * ((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
+    if (bn_env == 0 && p.force_splits <= 0 && tiles256 < sm_count && env_int("MNI_B200_PLAN_MODEL", 1) != 0) {
+        const double k_eff = static_cast<double>(p.K) * static_cast<double>(p.fold);
+        const double out_bytes = 4.0 * static_cast<double>(p.batch) * static_cast<double>(p.M) * static_cast<double>(p.N);
+        double best = 1e300;
+        for (int bn : {256, 128, 64}) {
+            if (bn > 64 && p.N <= bn / 2) continue;               // no tile wider than the output needs
+            const int cg = pair_for(bn);
+            const double c_ns = bn == 256 ? (cg == 2 ? 30.0 : 33.0) : (bn == 128 ? 15.4 : 13.5);
+            const long long tiles = static_cast<long long>(p.batch) * ((p.M + BM * cg - 1) / (BM * cg)) * ((p.N + bn - 1) / bn);
+            const long long slots = std::max(1, sm_count / cg);
+            for (int sp : {1, 2, 3, 4, 6, 8, 12, 16}) {
+                if (sp > 1 && (tiles * sp > slots || k_eff / sp < 64.0)) continue;
+                const double rounds = static_cast<double>((tiles * sp + slots - 1) / slots);
+                const double t = rounds * (k_eff / sp) * c_ns + (sp > 1 ? 1500.0 + (sp + 1) * out_bytes / 3000.0 : 0.0);
+                if (t < best) { best = t; pl.bn = bn; model_splits = sp; }
+            }
+        }
+    }
+    pl.cg = pair_for(pl.bn);
     pl.bk = (pl.bn == 256 && !p.fast_tf32) ? 16 : 32;
     const int bk_env = env_int("MNI_B200_BK", 0);
     if (bk_env == 16 || bk_env == 32) pl.bk = bk_env;
@@ -1050,6 +1076,8 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     int splits = 1;
     if (p.force_splits > 0) {
         splits = p.force_splits;
+    } else if (model_splits > 0) {
+        splits = model_splits;
     } else if (tiles * 2 <= slots && iters >= 8) {
         // Few output tiles and a long contraction: split K so that the whole GPU works.
         splits = static_cast<int>(std::min<long long>(slots / tiles, iters / 4));
