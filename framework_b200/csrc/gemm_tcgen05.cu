@@ -1,31 +1,37 @@
 // Tensor-core GEMM for sm_100a: C[M,N] = sum_k A[m,k] * B[n,k] on f32 storage.
 //
-// Data path of one CTA (persistent over output tiles, one CTA per SM):
+// Data path of one CTA (persistent over output tiles, one CTA per SM; 2 + NS + 8 warps):
 //
 //   warp 0      TMA producer: cp.async.bulk.tensor (5-D maps: matrix dims + batch dims) brings
 //               a 128 x BK tile of A and a BN x BK tile of B into a swizzled shared-memory
 //               stage.  K-major and MN-major operands differ only in the tensor map and the
 //               box list, so transposed / permuted operands are read in place -- no transposed
 //               copy is ever written.
-//   warps 2-5   split: for every f32 x of the landed stage, lo = x - trunc_tf32(x) (exact in
-//               f32) is written to a sibling buffer of identical layout (the split is position
-//               independent, so it needs no knowledge of the swizzle).  The landed tile itself
-//               serves as hi: the tensor core ignores the low 13 mantissa bits of a TF32
-//               operand (tests/test_matmul_gpu.py pins that behaviour).
-//   warp 1      one thread issues tcgen05.mma.kind::tf32 per 8-deep k-step:
-//               lo*hi, hi*lo, hi*hi into one f32 accumulator in TMEM ("3xTF32").  In the
-//               optional fast mode the split warps idle and one MMA per k-step is issued
-//               on the raw tile.  Issuing one MMA costs this thread ~120 cycles, about what
-//               a 128 x 256 x 8 MMA takes to execute, so the loop is fully unrolled and keeps
-//               its per-stage bookkeeping to a wait, a fence and a commit.
-//   warps 6-9   epilogue: tcgen05.ld of the 128 x BN accumulator (double buffered in TMEM, so it
-//               overlaps the next tile's main loop), bias add in registers, 128B-swizzled
-//               staging patch in shared memory, TMA store (or TMA reduce-add for C += ...) of
-//               32 x 32 boxes; the tensor map clips the M / N tails.  Split-K partials go
-//               through the same path into scratch.  Outputs whose row pitch is not a multiple
-//               of 16 bytes take a plain-store fallback.
+//   warps 2..   split (NS = 8 warps; 4 idle relays in single-pass mode): for every f32 x of the
+//               landed stage, lo = x - trunc_tf32(x) (exact in f32) is written to a sibling buffer
+//               of identical layout (the split is position independent, so it needs no knowledge
+//               of the swizzle).  The landed tile itself serves as hi: the tensor core ignores the
+//               low 13 mantissa bits of a TF32 operand (tests/test_matmul_gpu.py pins that).
+//               Narrow tiles (BN <= 128, lone CTA) instead move A into tensor memory: each thread
+//               reads 16 k-values of its row and stores hi and lo with tcgen05.st; only B keeps a
+//               lo copy in shared memory.
+//   warp 1      issues tcgen05.mma.kind::tf32 per 8-deep k-step: lo*hi, hi*lo, hi*hi into one f32
+//               accumulator in TMEM ("3xTF32"); one MMA on the raw tile in single-pass mode.  The
+//               warp runs its loop uniformly and predicates the issue with elect.sync, and it reads
+//               the next stage's barrier before queueing this stage's MMAs.
+//   last 8      epilogue, two warps per TMEM lane quarter, half of the tile's columns each:
+//               tcgen05.ld of the accumulator (double buffered in TMEM, so it overlaps the next
+//               tile's main loop), bias add in registers, 128B-swizzled staging patch, TMA store
+//               (or TMA reduce-add for C += ...) of 32 x 32 boxes; the tensor map clips the M / N
+//               tails.  Split-K partials go through the same path into scratch.  Outputs whose row
+//               pitch is not a multiple of 16 bytes take a plain-store fallback.
 //
-// Every wait on an mbarrier is bounded: after ~2 s worth of clock cycles the waiter
+// CG = 2: two CTAs of a cluster share a 256 x BN tile (cta_group::2 MMAs issued by the leader).
+// Work is dealt out as whole tiles, round-robin over the CTAs (pairs); a ragged last wave is cut
+// into equal ranges of k-blocks instead, and a tile shared by several CTAs is summed in slot order
+// by the CTA that holds its first k-blocks (flags in global memory, bounded waits).
+//
+// Every wait on an mbarrier or flag is bounded: after ~2 s worth of clock cycles the waiter
 // records a code in a global error word, raises a CTA-wide abort flag and all roles
 // drain to the common exit, where TMEM is released.  Nothing traps.
 #include "internal.h"
@@ -73,6 +79,12 @@ struct KParams {
     int store_pre;             // act mode: write the raw product through the first map as well
     unsigned int *err;
     unsigned long long *prof;  // optional role wait counters (null = off)
+    // Balanced tail ("stream-K"): tiles [sk_first_tile, tiles) are not dealt out whole; their k-blocks are
+    // cut into one contiguous range per CTA (pair), so a ragged last wave costs its share, not a full wave.
+    int sk;                    // 0 = off
+    int sk_first_tile;         // tiles below this index are dealt out whole, round-robin
+    float *sk_partial;         // one accumulator tile per CTA: [cta][epilogue warp][chunk][lane][32]
+    unsigned int *sk_flags;    // [cta][epilogue warp], 0 = empty, 1 = partial written
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -283,14 +295,20 @@ __device__ __forceinline__ float gelu_tanh_f(float v) {
     return 0.5f * v * (1.0f + tanhf(inner));
 }
 
+enum SegmentKind { kSegWhole = 0, kSegOwner = 1, kSegContrib = 2 };
+
 struct TileCoord {
     int bt, tm, tn, split, it0, it1;
+    int kind;        // SegmentKind: a whole tile, the first k-blocks of a shared tile (its owner), or later ones
+    int tile;        // flat tile index (shared tiles: to find the contributors)
 };
 
 __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit) {
     TileCoord t;
     const int tile = unit / p.splits;
     t.split = unit - tile * p.splits;
+    t.kind = kSegWhole;
+    t.tile = tile;
     const int per_batch = p.tiles_m * p.tiles_n;
     t.bt = tile / per_batch;
     const int r = tile - t.bt * per_batch;
@@ -312,13 +330,50 @@ __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit) {
     return t;
 }
 
-// Number of k-iterations of a unit; the only thing the MMA issuer and the split warps need to know.
-__device__ __forceinline__ int unit_iters(const KParams &p, int unit) {
-    const int total = p.fold * p.kiters;
-    if (p.splits == 1) return total;
-    const int split = unit % p.splits;
-    return static_cast<int>(static_cast<long long>(total) * (split + 1) / p.splits) -
-           static_cast<int>(static_cast<long long>(total) * split / p.splits);
+// The work of one CTA (pair), in the order every role walks it: whole tiles slot, slot + P, ... and then,
+// with the balanced tail on, this slot's contiguous range of the tail's k-blocks, which touches at most the
+// end of one tile (kSegContrib: its first k-blocks belong to a lower slot), whole tiles, and the beginning
+// of one tile (kSegOwner).
+struct WorkIter {
+    int unit, unit_step, unit_end;     // whole units
+    long long w, w1;                   // tail range in k-blocks, relative to the tail's first tile
+};
+__device__ __forceinline__ long long sk_range_begin(const KParams &p, int slot, int nslots) {
+    const long long total = static_cast<long long>(p.batch * p.tiles_m * p.tiles_n - p.sk_first_tile) * (p.fold * p.kiters);
+    return total * slot / nslots;
+}
+__device__ __forceinline__ WorkIter work_begin(const KParams &p, int slot, int nslots) {
+    WorkIter wi;
+    wi.unit = slot;
+    wi.unit_step = nslots;
+    wi.unit_end = p.sk ? p.sk_first_tile : p.batch * p.tiles_m * p.tiles_n * p.splits;
+    wi.w = wi.w1 = 0;
+    if (p.sk) {
+        wi.w = sk_range_begin(p, slot, nslots);
+        wi.w1 = sk_range_begin(p, slot + 1, nslots);
+    }
+    return wi;
+}
+__device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit);
+__device__ __forceinline__ bool work_next(const KParams &p, WorkIter &wi, TileCoord &t) {
+    if (wi.unit < wi.unit_end) {
+        t = decode_unit(p, wi.unit);
+        wi.unit += wi.unit_step;
+        return true;
+    }
+    if (wi.w < wi.w1) {
+        const int per_tile = p.fold * p.kiters;
+        const int rel = static_cast<int>(wi.w / per_tile);
+        const int it0 = static_cast<int>(wi.w - static_cast<long long>(rel) * per_tile);
+        const int it1 = static_cast<int>(min(static_cast<long long>(per_tile), it0 + (wi.w1 - wi.w)));
+        t = decode_unit(p, p.sk_first_tile + rel);          // splits == 1 here: unit == tile
+        t.it0 = it0;
+        t.it1 = it1;
+        t.kind = (it0 == 0 && it1 == per_tile) ? kSegWhole : (it0 == 0 ? kSegOwner : kSegContrib);
+        wi.w += it1 - it0;
+        return true;
+    }
+    return false;
 }
 
 __device__ __forceinline__ void batch_coords(int q, int cnt, int d1, int d2, int &c0, int &c1, int &c2) {
@@ -424,7 +479,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_units = p.batch * p.tiles_m * p.tiles_n * p.splits;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -438,10 +492,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             constexpr uint32_t CHUNK_BYTES = 128u * BK;   // one 32-wide MN chunk: BK k-rows of 128 bytes
             const uint32_t dstA0 = smem_u32(stage_base);
             uint32_t dstA = dstA0;
-            for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
-                const TileCoord t = decode_unit(p, unit);
+            WorkIter wi = work_begin(p, unit0, unit_step);
+            TileCoord t;
+            while (ok && work_next(p, wi, t)) {
                 int f = 0, kk = t.it0;
-                if (p.fold > 1 || p.splits > 1) {
+                if (p.fold > 1 || p.splits > 1 || p.sk) {
                     f = t.it0 / p.kiters;
                     kk = t.it0 - f * p.kiters;
                 }
@@ -504,8 +559,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // A lone CTA in single-pass mode consumes the TMA barrier directly; otherwise the split warps
             // (of both CTAs, for a pair) announce the stage on the leader's barrier.
             const uint32_t ready0 = (FAST && CG == 1) ? bar_full : bar_xform;
-            for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
-                const int iters = unit_iters(p, unit);
+            WorkIter wi = work_begin(p, unit0, unit_step);
+            TileCoord wt;
+            while (ok && work_next(p, wi, wt)) {
+                const int iters = wt.it1 - wt.it0;
                 const int buf = acc_it & 1;
                 const uint32_t acc_phase = (acc_it >> 1) & 1;
                 ok = mbar_wait_warp(bar_acc_empty + 8u * buf, acc_phase ^ 1u, abort_flag, p.err, 0x200u | buf, waited_acc, timed);
@@ -581,8 +638,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             constexpr int PER = (N4 + NT - 1) / NT;       // float4s per thread (the last round may be partial)
             constexpr bool EXACT = N4 % NT == 0;
             constexpr int U = !EXACT ? 1 : (PER % 4 == 0) ? 4 : (PER % 2 == 0 ? 2 : 1);
-            for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
-                const int iters = unit_iters(p, unit);
+            WorkIter wi = work_begin(p, unit0, unit_step);
+            TileCoord wt;
+            while (ok && work_next(p, wi, wt)) {
+                const int iters = wt.it1 - wt.it0;
                 for (int it = 0; it < iters; ++it) {
                     ok = mbar_wait(bar_full + 8u * stage, phase, abort_flag, p.err, 0x400u | stage, waited, timed);
                     if (!ok) break;
@@ -673,8 +732,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         long long waited = 0, t_ld = 0, t_wg = 0;
         const bool use_tma = p.epi_mode == kEpiTmaStore || p.epi_mode == kEpiTmaReduce;
         const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
-        for (int unit = unit0; ok && unit < total_units; unit += unit_step) {
-            const TileCoord t = decode_unit(p, unit);
+        WorkIter wi = work_begin(p, unit0, unit_step);
+        TileCoord t;
+        const int my_cta = static_cast<int>(blockIdx.x);                 // slot * CG + rank in the pair
+        while (ok && work_next(p, wi, t)) {
             const int buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
             ok = mbar_wait(bar_acc_full + 8u * buf, acc_phase, abort_flag, p.err, 0x500u | buf, waited, timed);
@@ -685,6 +746,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int row0 = t.tm * (BM * CG) + static_cast<int>(cta_rank) * BM + q * 32;
             const int cbatch = fuse ? t.bt : t.split * p.batch + t.bt;
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
+            // Shared tile of the balanced tail: the owner (first k-blocks) adds the accumulators of the slots
+            // above it, in slot order, before the usual epilogue; a contributor only parks its accumulator.
+            int n_contrib = 0;
+            if (t.kind == kSegOwner) {
+                const int nslots = static_cast<int>(gridDim.x) / CG;
+                const long long tile_end = static_cast<long long>(t.tile - p.sk_first_tile + 1) * (p.fold * p.kiters);
+                for (int j = unit0 + 1; j < nslots && sk_range_begin(p, j, nslots) < tile_end; ++j) ++n_contrib;
+            }
+            bool waited_contrib = false, parked = false;
             if (row0 < p.M) {
                 for (int chunk = chunk_lo; chunk < chunk_lo + CHUNKS; ++chunk) {
                     const int col0 = t.tn * BN + chunk * 32;
@@ -695,6 +765,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tmem_ld32_issue(tbase + chunk * 32, v);
                     tmem_ld_wait();
                     if (p.prof) t_ld += clock64() - t_ld0;
+                    if (t.kind == kSegContrib) {
+                        float4 *dst = reinterpret_cast<float4 *>(
+                            p.sk_partial + ((static_cast<size_t>(my_cta) * kEpiWarps + ew) * CHUNKS + (chunk - chunk_lo)) * 1024 + lane * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            __stcg(dst + j, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                        __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+                        parked = true;
+                        continue;
+                    }
+                    if (n_contrib > 0) {
+                        if (!waited_contrib) {
+                            // Bounded wait for every contributor's flag (they park their tile first thing in
+                            // their range, so this normally falls straight through).
+                            for (int c = 1; ok && c <= n_contrib; ++c) {
+                                const unsigned int *flag = p.sk_flags + (static_cast<size_t>(my_cta + c * CG) * kEpiWarps + ew);
+                                const long long tw0 = clock64();
+                                unsigned int seen = 0;
+                                while (true) {
+                                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+                                    if (seen != 0u) break;
+                                    if (*abort_flag || clock64() - tw0 > kWaitCycles) {
+                                        *abort_flag = 1u;
+                                        atomicCAS(p.err, 0u, 0x600u);
+                                        ok = false;
+                                        break;
+                                    }
+                                }
+                            }
+                            ok = __all_sync(0xffffffffu, ok);
+                            waited_contrib = true;
+                            if (!ok) break;
+                        }
+                        for (int c = 1; c <= n_contrib; ++c) {
+                            const float4 *src = reinterpret_cast<const float4 *>(
+                                p.sk_partial + ((static_cast<size_t>(my_cta + c * CG) * kEpiWarps + ew) * CHUNKS + (chunk - chunk_lo)) * 1024 + lane * 32);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float4 x = __ldcg(src + j);
+                                v[4 * j + 0] = __float_as_uint(__uint_as_float(v[4 * j + 0]) + x.x);
+                                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + x.y);
+                                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + x.z);
+                                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + x.w);
+                            }
+                        }
+                    }
                     // Stages the 32 values of this lane's row into the warp's next patch and hands the
                     // patch to the TMA unit (store, or reduce-add for C += ...).
                     auto emit = [&](const CUtensorMap *map, bool reduce) {
@@ -789,6 +905,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                     }
                 }
+            }
+            if (!ok) break;
+            if (parked) {
+                // publish: every lane's stores are fenced, then one release store of the flag
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    unsigned int *flag = p.sk_flags + (static_cast<size_t>(my_cta) * kEpiWarps + ew);
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
+                }
+            } else if (waited_contrib) {
+                // every lane has read the partials; put the flags back to empty for the next launch
+                __syncwarp();
+                if (lane == 0)
+                    for (int c = 1; c <= n_contrib; ++c)
+                        p.sk_flags[static_cast<size_t>(my_cta + c * CG) * kEpiWarps + ew] = 0u;
             }
             tc_fence_before();
             __syncwarp();
@@ -1001,6 +1133,8 @@ struct Plan {
     int bn, bk, cg, stages, splits, tiles_m, tiles_n, grid;   // cg = CTAs per tile (1, or 2 = CTA pair)
     int patches;                                              // epilogue staging patches per warp
     bool ta;                                                  // A operand of the MMAs from tensor memory
+    bool sk;                                                  // balanced tail: the last, ragged wave is cut by k-blocks
+    int sk_first_tile;
     size_t smem;
 };
 
@@ -1086,6 +1220,20 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     pl.splits = splits;
     const long long units = tiles * splits;
     pl.grid = static_cast<int>(std::min<long long>(units, slots)) * pl.cg;
+    // Balanced tail: when the last wave of whole tiles would leave more than 8 % of the slots idle, its
+    // k-blocks are dealt out evenly instead (every slot gets one contiguous range; tiles cut by a range
+    // boundary are summed in the owner's epilogue, in slot order).
+    pl.sk = false;
+    pl.sk_first_tile = 0;
+    if (splits == 1 && p.D == nullptr && env_int("MNI_B200_STREAMK", 0) != 0) {
+        const long long full_rounds = tiles / slots, rem = tiles - full_rounds * slots;
+        const double eff = static_cast<double>(tiles) / static_cast<double>((full_rounds + 1) * slots);
+        if (rem > 0 && eff < 0.92 && iters >= 8 && rem * iters / slots >= 8 && tiles * 2 > slots) {
+            pl.sk = true;
+            pl.sk_first_tile = static_cast<int>(full_rounds * slots);
+            pl.grid = static_cast<int>(slots) * pl.cg;
+        }
+    }
     return pl;
 }
 
@@ -1120,6 +1268,25 @@ cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtenso
 }
 
 }  // namespace
+
+// Flags of the balanced tail: one per (CTA, epilogue warp); a contributor sets its flag after parking its
+// accumulator, the owner of the tile clears it after reading, so the array is all zero between launches.
+constexpr int kSkFlagCount = 256 * kEpiWarps;
+__device__ unsigned int g_sk_flags[kSkFlagCount];
+
+unsigned int *sk_flags_ptr() {
+    static thread_local int cached_dev = -1;
+    static thread_local unsigned int *ptr = nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    if (dev != cached_dev) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_sk_flags) != cudaSuccess) return nullptr;
+        ptr = static_cast<unsigned int *>(p);
+        cached_dev = dev;
+    }
+    return ptr;
+}
 
 // Role wait counters (diagnostics): cycles summed over CTAs that each role spent blocked.
 __device__ unsigned long long g_role_waits[8];
@@ -1156,6 +1323,7 @@ bool gemm_tc_can_fuse_activation(const GemmProblem &p, int sm_count) {
 
 size_t gemm_tc_partial_bytes(const GemmProblem &p, int sm_count) {
     const Plan pl = make_plan(p, sm_count);
+    if (pl.sk) return static_cast<size_t>(pl.grid) * BM * pl.bn * sizeof(float);   // one parked accumulator per CTA
     if (pl.splits <= 1) return 0;
     return static_cast<size_t>(pl.splits) * p.batch * p.M * p.N * sizeof(float);
 }
@@ -1165,7 +1333,7 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     if (p.M <= 0 || p.N <= 0 || p.batch <= 0) return MNI_B200_OK;
     const Plan pl = make_plan(p, sm_count);
     if (p.K <= 0) return fail(MNI_B200_ERR_ARG, "empty contraction reached the tensor-core launcher");
-    if (pl.splits > 1 && partial == nullptr)
+    if ((pl.splits > 1 || pl.sk) && partial == nullptr)
         return fail(MNI_B200_ERR_WORKSPACE, "split-K launch without partial storage");
 
     KParams k{};
@@ -1247,6 +1415,15 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     k.accumulate = p.accumulate;
     k.err = err_word;
     k.prof = env_int("MNI_B200_ROLE_WAITS", 0) ? role_wait_ptr() : nullptr;
+    k.sk = pl.sk ? 1 : 0;
+    k.sk_first_tile = pl.sk_first_tile;
+    k.sk_partial = pl.sk ? partial : nullptr;
+    k.sk_flags = nullptr;
+    if (pl.sk) {
+        k.sk_flags = sk_flags_ptr();
+        if (!k.sk_flags) return fail(MNI_B200_ERR_CUDA, "balanced-tail flags unavailable");
+        if (pl.grid * kEpiWarps > kSkFlagCount) return fail(MNI_B200_ERR_CUDA, "balanced-tail flag array too small");
+    }
 
     cudaError_t e = cudaErrorInvalidValue;
     const int split_warps = env_int("MNI_B200_SPLIT_WARPS", 8);

@@ -377,3 +377,55 @@ def test_small_backward_side_stream_inside_a_cuda_graph(F, oracle):
         assert np.max(np.abs(da.numpy() - ra.numpy())) <= tol_3xtf32(72, g2, b)
         assert np.max(np.abs(db.numpy() - rb.numpy())) <= tol_3xtf32(96, a, g2)
     F.device_status()
+
+
+@pytest.mark.parametrize("shape_a,shape_b,flags,bias", [
+    ((1536, 512), (512, 2048), 0, False),            # 48 pair-tiles on 74 pairs: every tile is cut 2-3 ways
+    ((2560, 1024), (1024, 2304), 0, True),           # one whole round, then a 16-tile tail dealt out by k-blocks
+    ((24, 512, 512), (24, 512, 64), 0, False),       # 64-wide tiles (A from tensor memory), 96 tiles on 148 CTAs
+    ((1536, 512), (512, 2048), 1, False),            # single-pass TF32 mode
+])
+def test_balanced_tail_matches_oracle(F, oracle, shape_a, shape_b, flags, bias):
+    """Shapes whose last wave of tiles is ragged: the tail's k-blocks are dealt out evenly and shared tiles are
+    summed in the owner's epilogue.  Forward (with bias) and both gradients against the CPU backend."""
+    rng = np.random.default_rng(sum(shape_a) + sum(shape_b))
+    a = rng.standard_normal(shape_a, dtype=np.float32)
+    b = rng.standard_normal(shape_b, dtype=np.float32)
+    bv = rng.standard_normal(shape_b[-1], dtype=np.float32) if bias else None
+    H = oracle.HostTensor
+    ref = oracle.matmul(H.from_array(a), H.from_array(b)).numpy()
+    if bias:
+        ref = ref + bv
+    out = F.matmul(F.DeviceTensor.from_numpy(a), F.DeviceTensor.from_numpy(b),
+                   F.DeviceTensor.from_numpy(bv) if bias else None, flags=flags)
+    F.device_status()
+    k = shape_a[-1]
+    if flags & 1:
+        assert rel_fro(out.numpy(), ref) <= 2e-3
+    else:
+        assert float(np.max(np.abs(out.numpy() - ref))) <= tol_3xtf32(k, a, b) + 1e-6
+    g = rng.standard_normal(ref.shape, dtype=np.float32)
+    da, db = F.matmul_backward(F.DeviceTensor.from_numpy(g), F.DeviceTensor.from_numpy(a), F.DeviceTensor.from_numpy(b),
+                               flags=flags)
+    F.device_status()
+    ra, rb = oracle.matmul_backward(H.from_array(g), H.from_array(a), H.from_array(b))
+    if flags & 1:
+        assert rel_fro(da.numpy(), ra.numpy()) <= 2e-3 and rel_fro(db.numpy(), rb.numpy()) <= 2e-3
+    else:
+        assert float(np.max(np.abs(da.numpy() - ra.numpy()))) <= tol_3xtf32(shape_b[-1], g, b)
+        kb = shape_a[-2] * (int(np.prod(shape_a[:-2])) if len(shape_b) == 2 else 1)
+        assert float(np.max(np.abs(db.numpy() - rb.numpy()))) <= tol_3xtf32(kb, a, g)
+
+
+def test_balanced_tail_is_reproducible_and_leaves_flags_clear(F):
+    """Two runs of a cut-tile product are bit-identical (fixed summation order) and so is a third after other
+    launches: the flags the contributors raise are cleared by the owners."""
+    rng = np.random.default_rng(77)
+    a = F.DeviceTensor.from_numpy(rng.standard_normal((1536, 512), dtype=np.float32))
+    b = F.DeviceTensor.from_numpy(rng.standard_normal((512, 2048), dtype=np.float32))
+    first = F.matmul(a, b).numpy()
+    second = F.matmul(a, b).numpy()
+    F.matmul(b.permute((1, 0)), a.permute((1, 0)))          # another cut-tile launch in between
+    third = F.matmul(a, b).numpy()
+    F.device_status()
+    assert np.array_equal(first, second) and np.array_equal(first, third)
