@@ -45,6 +45,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int kMaxStages = 8;
+constexpr int kSkMaxShare = 6;                             // balanced tail: most units that may share one tile
 constexpr int kEpiWarps = 8;                                // two per TMEM lane quarter, half of the columns each
 constexpr int kEpiBufBytes = 32 * 128;                     // one 32 x 32 f32 patch
 constexpr int kBarBytes = (3 * kMaxStages + 4) * 8 + 16;
@@ -83,8 +84,8 @@ struct KParams {
     // cut into one contiguous range per CTA (pair), so a ragged last wave costs its share, not a full wave.
     int sk;                    // 0 = off
     int sk_first_tile;         // tiles below this index are dealt out whole, round-robin
-    float *sk_partial;         // one accumulator tile per CTA: [cta][epilogue warp][chunk][lane][32]
-    unsigned int *sk_flags;    // [cta][epilogue warp], 0 = empty, 1 = partial written
+    float *sk_partial;         // two parked accumulator tiles per CTA: [cta][2][epilogue warp][chunk][8][lane] float4
+    unsigned int *sk_flags;    // ready flags [cta][2][epilogue warp] (1 = parked), then tickets [tile][rank][epilogue warp]
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -295,19 +296,19 @@ __device__ __forceinline__ float gelu_tanh_f(float v) {
     return 0.5f * v * (1.0f + tanhf(inner));
 }
 
-enum SegmentKind { kSegWhole = 0, kSegOwner = 1, kSegContrib = 2 };
-
 struct TileCoord {
     int bt, tm, tn, split, it0, it1;
-    int kind;        // SegmentKind: a whole tile, the first k-blocks of a shared tile (its owner), or later ones
-    int tile;        // flat tile index (shared tiles: to find the contributors)
+    int shared;      // balanced tail: this unit is only a range of the tile's k-blocks
+    int park;        // shared: which of the CTA's two parking places it uses (0 = first unit of its range)
+    int tile;        // flat tile index
 };
 
 __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit) {
     TileCoord t;
     const int tile = unit / p.splits;
     t.split = unit - tile * p.splits;
-    t.kind = kSegWhole;
+    t.shared = 0;
+    t.park = 0;
     t.tile = tile;
     const int per_batch = p.tiles_m * p.tiles_n;
     t.bt = tile / per_batch;
@@ -332,11 +333,10 @@ __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit) {
 
 // The work of one CTA (pair), in the order every role walks it: whole tiles slot, slot + P, ... and then,
 // with the balanced tail on, this slot's contiguous range of the tail's k-blocks, which touches at most the
-// end of one tile (kSegContrib: its first k-blocks belong to a lower slot), whole tiles, and the beginning
-// of one tile (kSegOwner).
+// end of one tile, whole tiles, and the beginning of one tile.
 struct WorkIter {
     int unit, unit_step, unit_end;     // whole units
-    long long w, w1;                   // tail range in k-blocks, relative to the tail's first tile
+    long long w0, w, w1;               // tail range in k-blocks, relative to the tail's first tile
 };
 __device__ __forceinline__ long long sk_range_begin(const KParams &p, int slot, int nslots) {
     const long long total = static_cast<long long>(p.batch * p.tiles_m * p.tiles_n - p.sk_first_tile) * (p.fold * p.kiters);
@@ -347,9 +347,9 @@ __device__ __forceinline__ WorkIter work_begin(const KParams &p, int slot, int n
     wi.unit = slot;
     wi.unit_step = nslots;
     wi.unit_end = p.sk ? p.sk_first_tile : p.batch * p.tiles_m * p.tiles_n * p.splits;
-    wi.w = wi.w1 = 0;
+    wi.w0 = wi.w = wi.w1 = 0;
     if (p.sk) {
-        wi.w = sk_range_begin(p, slot, nslots);
+        wi.w0 = wi.w = sk_range_begin(p, slot, nslots);
         wi.w1 = sk_range_begin(p, slot + 1, nslots);
     }
     return wi;
@@ -369,7 +369,8 @@ __device__ __forceinline__ bool work_next(const KParams &p, WorkIter &wi, TileCo
         t = decode_unit(p, p.sk_first_tile + rel);          // splits == 1 here: unit == tile
         t.it0 = it0;
         t.it1 = it1;
-        t.kind = (it0 == 0 && it1 == per_tile) ? kSegWhole : (it0 == 0 ? kSegOwner : kSegContrib);
+        t.shared = (it0 != 0 || it1 != per_tile) ? 1 : 0;
+        t.park = wi.w == wi.w0 ? 0 : 1;
         wi.w += it1 - it0;
         return true;
     }
@@ -746,15 +747,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int row0 = t.tm * (BM * CG) + static_cast<int>(cta_rank) * BM + q * 32;
             const int cbatch = fuse ? t.bt : t.split * p.batch + t.bt;
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
-            // Shared tile of the balanced tail: the owner (first k-blocks) adds the accumulators of the slots
-            // above it, in slot order, before the usual epilogue; a contributor only parks its accumulator.
-            int n_contrib = 0;
-            if (t.kind == kSegOwner) {
-                const int nslots = static_cast<int>(gridDim.x) / CG;
-                const long long tile_end = static_cast<long long>(t.tile - p.sk_first_tile + 1) * (p.fold * p.kiters);
-                for (int j = unit0 + 1; j < nslots && sk_range_begin(p, j, nslots) < tile_end; ++j) ++n_contrib;
+            // Shared tile of the balanced tail.  Each (tile, CTA rank, epilogue warp) region has a ticket; the
+            // units of the tile arrive in any order, all but the last park their accumulator (and raise a
+            // ready flag), the last one adds the parked ones to its own in slot order -- the sum does not
+            // depend on who came last -- and runs the usual epilogue.
+            int seg_first = 0, seg_count = 1;          // slots sharing the tile: seg_first .. seg_first + seg_count - 1
+            bool reducer = false;
+            const int nslots = static_cast<int>(gridDim.x) / CG;
+            if (t.shared) {
+                const long long per_tile = p.fold * p.kiters;
+                const long long tile_begin = static_cast<long long>(t.tile - p.sk_first_tile) * per_tile;
+                const long long tile_end = tile_begin + per_tile;
+                seg_first = unit0;
+                while (seg_first > 0 && sk_range_begin(p, seg_first, nslots) > tile_begin) --seg_first;
+                int last = unit0;
+                while (last + 1 < nslots && sk_range_begin(p, last + 1, nslots) < tile_end) ++last;
+                seg_count = last - seg_first + 1;
             }
             bool waited_contrib = false, parked = false;
+            unsigned int *ticket = nullptr;
+            if (t.shared && seg_count > 1 && row0 < p.M && t.tn * BN + chunk_lo * 32 < p.N) {
+                const size_t region = (static_cast<size_t>(t.tile - p.sk_first_tile) * CG + cta_rank) * kEpiWarps + ew;
+                ticket = p.sk_flags + static_cast<size_t>(gridDim.x) * 2 * kEpiWarps + region;
+                unsigned int old = 0;
+                if (lane == 0) old = atomicAdd(ticket, 1u);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                reducer = old == static_cast<unsigned int>(seg_count - 1);
+            }
+            const bool park_it = t.shared && seg_count > 1 && !reducer;
+            // The reducer's list of the tile's other units, in slot order: index of their parking place
+            // ((cta * 2 + place) * warps + warp, also the index of its ready flag).
+            size_t others[kSkMaxShare - 1];
+            int n_others = 0, n_before = 0;
+            if (reducer) {
+                const long long tile_begin = static_cast<long long>(t.tile - p.sk_first_tile) * (p.fold * p.kiters);
+                for (int j = seg_first; j < seg_first + seg_count; ++j) {
+                    if (j == unit0) continue;
+                    const int idx = (j == seg_first && sk_range_begin(p, j, nslots) < tile_begin) ? 1 : 0;
+                    others[n_others++] = (static_cast<size_t>(j * CG + static_cast<int>(cta_rank)) * 2 + idx) * kEpiWarps + ew;
+                    if (j < unit0) ++n_before;
+                }
+            }
             if (row0 < p.M) {
                 for (int chunk = chunk_lo; chunk < chunk_lo + CHUNKS; ++chunk) {
                     const int col0 = t.tn * BN + chunk * 32;
@@ -765,22 +798,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tmem_ld32_issue(tbase + chunk * 32, v);
                     tmem_ld_wait();
                     if (p.prof) t_ld += clock64() - t_ld0;
-                    if (t.kind == kSegContrib) {
+                    if (park_it) {
+                        // [j][lane] order: one instruction of the warp writes 512 contiguous bytes
                         float4 *dst = reinterpret_cast<float4 *>(
-                            p.sk_partial + ((static_cast<size_t>(my_cta) * kEpiWarps + ew) * CHUNKS + (chunk - chunk_lo)) * 1024 + lane * 32);
+                            p.sk_partial + (((static_cast<size_t>(my_cta) * 2 + t.park) * kEpiWarps + ew) * CHUNKS + (chunk - chunk_lo)) * 1024) + lane;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            __stcg(dst + j, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                            __stcg(dst + j * 32, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                                                         __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
                         parked = true;
                         continue;
                     }
-                    if (n_contrib > 0) {
+                    if (reducer) {
                         if (!waited_contrib) {
-                            // Bounded wait for every contributor's flag (they park their tile first thing in
-                            // their range, so this normally falls straight through).
-                            for (int c = 1; ok && c <= n_contrib; ++c) {
-                                const unsigned int *flag = p.sk_flags + (static_cast<size_t>(my_cta + c * CG) * kEpiWarps + ew);
+                            // Bounded wait for the ready flag of every other unit of the tile (they took their
+                            // tickets earlier, so they are at most one parking pass behind).
+                            for (int o = 0; ok && o < n_others; ++o) {
+                                const unsigned int *flag = p.sk_flags + others[o];
                                 const long long tw0 = clock64();
                                 unsigned int seen = 0;
                                 while (true) {
@@ -798,16 +832,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             waited_contrib = true;
                             if (!ok) break;
                         }
-                        for (int c = 1; c <= n_contrib; ++c) {
-                            const float4 *src = reinterpret_cast<const float4 *>(
-                                p.sk_partial + ((static_cast<size_t>(my_cta + c * CG) * kEpiWarps + ew) * CHUNKS + (chunk - chunk_lo)) * 1024 + lane * 32);
+                        // Sum in slot (= ascending k) order; this warp's own accumulator takes its place in it.
+                        // Each parked tile is fetched with independent 16-byte loads, half a chunk at a time.
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const float4 x = __ldcg(src + j);
-                                v[4 * j + 0] = __float_as_uint(__uint_as_float(v[4 * j + 0]) + x.x);
-                                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + x.y);
-                                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + x.z);
-                                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + x.w);
+                        for (int h = 0; h < 2; ++h) {
+                            float4 pre[4];
+                            for (int o = 0; o < n_before; ++o) {
+                                const float4 *src = reinterpret_cast<const float4 *>(
+                                                        p.sk_partial + (others[o] * CHUNKS + (chunk - chunk_lo)) * 1024) + h * 128 + lane;
+                                float4 x[4];
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) x[u] = __ldcg(src + u * 32);
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    if (o == 0) pre[u] = x[u];
+                                    else { pre[u].x += x[u].x; pre[u].y += x[u].y; pre[u].z += x[u].z; pre[u].w += x[u].w; }
+                                }
+                            }
+                            if (n_before > 0) {
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    const int b = 16 * h + 4 * u;
+                                    v[b + 0] = __float_as_uint(pre[u].x + __uint_as_float(v[b + 0]));
+                                    v[b + 1] = __float_as_uint(pre[u].y + __uint_as_float(v[b + 1]));
+                                    v[b + 2] = __float_as_uint(pre[u].z + __uint_as_float(v[b + 2]));
+                                    v[b + 3] = __float_as_uint(pre[u].w + __uint_as_float(v[b + 3]));
+                                }
+                            }
+                            for (int o = n_before; o < n_others; ++o) {
+                                const float4 *src = reinterpret_cast<const float4 *>(
+                                                        p.sk_partial + (others[o] * CHUNKS + (chunk - chunk_lo)) * 1024) + h * 128 + lane;
+                                float4 x[4];
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) x[u] = __ldcg(src + u * 32);
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    const int b = 16 * h + 4 * u;
+                                    v[b + 0] = __float_as_uint(__uint_as_float(v[b + 0]) + x[u].x);
+                                    v[b + 1] = __float_as_uint(__uint_as_float(v[b + 1]) + x[u].y);
+                                    v[b + 2] = __float_as_uint(__uint_as_float(v[b + 2]) + x[u].z);
+                                    v[b + 3] = __float_as_uint(__uint_as_float(v[b + 3]) + x[u].w);
+                                }
                             }
                         }
                     }
@@ -908,19 +973,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             if (!ok) break;
             if (parked) {
-                // publish: every lane's stores are fenced, then one release store of the flag
+                // publish: every lane's stores are fenced, then one release store of the ready flag
                 __threadfence();
                 __syncwarp();
                 if (lane == 0) {
-                    unsigned int *flag = p.sk_flags + (static_cast<size_t>(my_cta) * kEpiWarps + ew);
+                    unsigned int *flag = p.sk_flags + ((static_cast<size_t>(my_cta) * 2 + t.park) * kEpiWarps + ew);
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
                 }
-            } else if (waited_contrib) {
-                // every lane has read the partials; put the flags back to empty for the next launch
+            } else if (reducer) {
+                // every lane has read the parked tiles: ticket and ready flags go back to zero for the next launch
                 __syncwarp();
-                if (lane == 0)
-                    for (int c = 1; c <= n_contrib; ++c)
-                        p.sk_flags[static_cast<size_t>(my_cta + c * CG) * kEpiWarps + ew] = 0u;
+                if (lane == 0) {
+                    *ticket = 0u;
+                    if (waited_contrib)
+                        for (int o = 0; o < n_others; ++o) p.sk_flags[others[o]] = 0u;
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -1228,10 +1295,16 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     if (splits == 1 && p.D == nullptr && env_int("MNI_B200_STREAMK", 0) != 0) {
         const long long full_rounds = tiles / slots, rem = tiles - full_rounds * slots;
         const double eff = static_cast<double>(tiles) / static_cast<double>((full_rounds + 1) * slots);
-        if (rem > 0 && eff < 0.92 && iters >= 8 && rem * iters / slots >= 8 && tiles * 2 > slots) {
-            pl.sk = true;
-            pl.sk_first_tile = static_cast<int>(full_rounds * slots);
-            pl.grid = static_cast<int>(slots) * pl.cg;
+        if (rem > 0 && eff < 0.92 && iters >= 8 && tiles * 2 > slots) {
+            // the tail takes one whole round along when there is one, so that a range is at least a tile long
+            const long long whole = full_rounds > 0 ? full_rounds - 1 : 0;
+            const long long range = (tiles - whole * slots) * iters / slots;
+            // a tile is shared by at most iters / range + 2 units
+            if (range >= 8 && iters / range + 2 <= kSkMaxShare) {
+                pl.sk = true;
+                pl.sk_first_tile = static_cast<int>(whole * slots);
+                pl.grid = static_cast<int>(slots) * pl.cg;
+            }
         }
     }
     return pl;
@@ -1269,9 +1342,10 @@ cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtenso
 
 }  // namespace
 
-// Flags of the balanced tail: one per (CTA, epilogue warp); a contributor sets its flag after parking its
-// accumulator, the owner of the tile clears it after reading, so the array is all zero between launches.
-constexpr int kSkFlagCount = 256 * kEpiWarps;
+// Flags of the balanced tail: per (CTA, parking place, epilogue warp) a ready flag, raised after an accumulator
+// is parked, and per region of a tail tile a ticket; the unit that reduces a tile clears what it used, so the
+// array is all zero between launches.
+constexpr int kSkFlagCount = 3 * 256 * kEpiWarps;
 __device__ unsigned int g_sk_flags[kSkFlagCount];
 
 unsigned int *sk_flags_ptr() {
@@ -1323,7 +1397,7 @@ bool gemm_tc_can_fuse_activation(const GemmProblem &p, int sm_count) {
 
 size_t gemm_tc_partial_bytes(const GemmProblem &p, int sm_count) {
     const Plan pl = make_plan(p, sm_count);
-    if (pl.sk) return static_cast<size_t>(pl.grid) * BM * pl.bn * sizeof(float);   // one parked accumulator per CTA
+    if (pl.sk) return static_cast<size_t>(pl.grid) * 2 * BM * pl.bn * sizeof(float);   // two parked accumulators per CTA
     if (pl.splits <= 1) return 0;
     return static_cast<size_t>(pl.splits) * p.batch * p.M * p.N * sizeof(float);
 }
@@ -1422,7 +1496,8 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     if (pl.sk) {
         k.sk_flags = sk_flags_ptr();
         if (!k.sk_flags) return fail(MNI_B200_ERR_CUDA, "balanced-tail flags unavailable");
-        if (pl.grid * kEpiWarps > kSkFlagCount) return fail(MNI_B200_ERR_CUDA, "balanced-tail flag array too small");
+        // ready flags for 2 parking places per CTA, then one ticket per region of a tail tile (fewer tiles than CTAs)
+        if (pl.grid * 3 * kEpiWarps > kSkFlagCount) return fail(MNI_B200_ERR_CUDA, "balanced-tail flag array too small");
     }
 
     cudaError_t e = cudaErrorInvalidValue;

@@ -385,9 +385,11 @@ def test_small_backward_side_stream_inside_a_cuda_graph(F, oracle):
     ((24, 512, 512), (24, 512, 64), 0, False),       # 64-wide tiles (A from tensor memory), 96 tiles on 148 CTAs
     ((1536, 512), (512, 2048), 1, False),            # single-pass TF32 mode
 ])
-def test_balanced_tail_matches_oracle(F, oracle, shape_a, shape_b, flags, bias):
-    """Shapes whose last wave of tiles is ragged: the tail's k-blocks are dealt out evenly and shared tiles are
-    summed in the owner's epilogue.  Forward (with bias) and both gradients against the CPU backend."""
+def test_balanced_tail_matches_oracle(F, oracle, monkeypatch, shape_a, shape_b, flags, bias):
+    """Shapes whose last wave of tiles is ragged, with the balanced tail switched on (it is opt-in): the tail's
+    k-blocks are dealt out evenly and a tile shared by several CTAs is summed in the epilogue of the last one
+    to arrive.  Forward (with bias) and both gradients against the CPU backend."""
+    monkeypatch.setenv("MNI_B200_STREAMK", "1")
     rng = np.random.default_rng(sum(shape_a) + sum(shape_b))
     a = rng.standard_normal(shape_a, dtype=np.float32)
     b = rng.standard_normal(shape_b, dtype=np.float32)
@@ -417,9 +419,11 @@ def test_balanced_tail_matches_oracle(F, oracle, shape_a, shape_b, flags, bias):
         assert float(np.max(np.abs(db.numpy() - rb.numpy()))) <= tol_3xtf32(kb, a, g)
 
 
-def test_balanced_tail_is_reproducible_and_leaves_flags_clear(F):
-    """Two runs of a cut-tile product are bit-identical (fixed summation order) and so is a third after other
-    launches: the flags the contributors raise are cleared by the owners."""
+def test_balanced_tail_is_reproducible_and_leaves_flags_clear(F, monkeypatch):
+    """Two runs of a cut-tile product are bit-identical (fixed summation order, whoever arrives last) and so is a
+    third after other launches: tickets and ready flags are cleared by the reducing CTA.  The result also agrees
+    with the whole-tile schedule to rounding."""
+    monkeypatch.setenv("MNI_B200_STREAMK", "1")
     rng = np.random.default_rng(77)
     a = F.DeviceTensor.from_numpy(rng.standard_normal((1536, 512), dtype=np.float32))
     b = F.DeviceTensor.from_numpy(rng.standard_normal((512, 2048), dtype=np.float32))
@@ -429,3 +433,6 @@ def test_balanced_tail_is_reproducible_and_leaves_flags_clear(F):
     third = F.matmul(a, b).numpy()
     F.device_status()
     assert np.array_equal(first, second) and np.array_equal(first, third)
+    monkeypatch.setenv("MNI_B200_STREAMK", "0")
+    whole = F.matmul(a, b).numpy()
+    assert rel_fro(first, whole) < 1e-6
