@@ -248,26 +248,33 @@ skinny_dx_kernel(const float *__restrict__ dy, long long lddy, const float *__re
     const float *w0 = W + k0 * ldw;
     const bool row1 = k0 + 1 < K;
     const float *w1 = row1 ? w0 + ldw : w0;
-    for (long long n = lane * 4; n < N; n += 256) {
-        const long long n2 = n + 128;
-        const bool second = n2 < N;
-        float4 wa = __ldcs(reinterpret_cast<const float4 *>(w0 + n));
-        float4 wb = __ldcs(reinterpret_cast<const float4 *>(w1 + n));
-        float4 wc = make_float4(0.f, 0.f, 0.f, 0.f), wd = wc;
-        if (second) {
-            wc = __ldcs(reinterpret_cast<const float4 *>(w0 + n2));
-            wd = __ldcs(reinterpret_cast<const float4 *>(w1 + n2));
+    // 512 floats of both rows per step: eight 16-byte weight loads in flight per lane (4 KB per warp),
+    // enough outstanding bytes per SM to keep HBM busy with 16 resident warps.
+    constexpr int P = 4;                                   // 128-float positions per step
+    for (long long n = lane * 4; n < N; n += 128 * P) {
+        float4 wa[P], wb[P];
+#pragma unroll
+        for (int q = 0; q < P; ++q) {
+            const long long nq = n + 128 * q;
+            if (nq < N) {
+                wa[q] = __ldcs(reinterpret_cast<const float4 *>(w0 + nq));
+                wb[q] = __ldcs(reinterpret_cast<const float4 *>(w1 + nq));
+            } else {
+                wa[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                wb[q] = wa[q];
+            }
         }
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             if (m < M) {
-                const float4 g = __ldg(reinterpret_cast<const float4 *>(dy + m * lddy + n));
-                acc[0][m] = fmaf(g.x, wa.x, fmaf(g.y, wa.y, fmaf(g.z, wa.z, fmaf(g.w, wa.w, acc[0][m]))));
-                acc[1][m] = fmaf(g.x, wb.x, fmaf(g.y, wb.y, fmaf(g.z, wb.z, fmaf(g.w, wb.w, acc[1][m]))));
-                if (second) {
-                    const float4 h = __ldg(reinterpret_cast<const float4 *>(dy + m * lddy + n2));
-                    acc[0][m] = fmaf(h.x, wc.x, fmaf(h.y, wc.y, fmaf(h.z, wc.z, fmaf(h.w, wc.w, acc[0][m]))));
-                    acc[1][m] = fmaf(h.x, wd.x, fmaf(h.y, wd.y, fmaf(h.z, wd.z, fmaf(h.w, wd.w, acc[1][m]))));
+#pragma unroll
+                for (int q = 0; q < P; ++q) {
+                    const long long nq = n + 128 * q;
+                    if (nq < N) {
+                        const float4 g = __ldg(reinterpret_cast<const float4 *>(dy + m * lddy + nq));
+                        acc[0][m] = fmaf(g.x, wa[q].x, fmaf(g.y, wa[q].y, fmaf(g.z, wa[q].z, fmaf(g.w, wa[q].w, acc[0][m]))));
+                        acc[1][m] = fmaf(g.x, wb[q].x, fmaf(g.y, wb[q].y, fmaf(g.z, wb[q].z, fmaf(g.w, wb[q].w, acc[1][m]))));
+                    }
                 }
             }
         }

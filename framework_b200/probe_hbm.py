@@ -4,7 +4,7 @@
 
 Algorithmic bytes: softmax forward 8 B/element (read x, write out), backward 12 B/element; gradient sum of
 squares 4 B/element; AdamW step 28 B/element (32 with the clipped gradient written back); skinny products
-one pass over the weight.  Timing is CUDA events around ``iters`` back-to-back calls after 3 warm-up calls.
+one pass over the weight.  Timing is CUDA events around a CUDA-graph replay of ``iters`` back-to-back calls after 3 warm-up calls.
 The same command under ``ncu -k regex:...`` gives the per-kernel DRAM counters.
 """
 from __future__ import annotations
@@ -23,16 +23,25 @@ def _tensor(*shape) -> F.DeviceTensor:
 
 
 def _time(fn, iters: int) -> float:
-    for _ in range(3):
-        fn()
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(iters):
-        fn()
-    stop.record()
-    torch.cuda.synchronize()
-    return start.elapsed_time(stop) / iters * 1e-3          # seconds per call
+    """Seconds per call: `iters` calls captured into one CUDA graph and replayed, so that launch latency of the
+    host interpreter does not hide a 10 us kernel."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(iters):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+    return start.elapsed_time(stop) / iters * 1e-3
 
 
 def _report(name: str, nbytes: float, seconds: float) -> None:
