@@ -438,7 +438,7 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None,
+            "scaling": "strong" if base.name in ("c4", "c5a") else "weak", "vs_baseline": None,
             "dtype": "f32 storage, 3xTF32 tensor-core arithmetic (f32 accumulate)" if args.precision != "tf32"
                      else "f32 storage, single-pass TF32 arithmetic (reduced precision mode)",
             "data": "synthetic (seeded numpy default_rng: x~U[0,1), W~N(0,0.02), b~N(0,0.02), dy~N(0,1))"

@@ -404,7 +404,9 @@ __device__ __forceinline__ void load_operand(int mode, uint32_t dst, const CUten
 // The split warps read each landed A row once, and store hi and lo with tcgen05.st into a TMEM slot
 // of the stage (columns 2*BN + stage*64: 32 of hi, 32 of lo); no lo copy of A is written to shared
 // memory and no MMA re-reads A from it, which is what bounds narrow tiles otherwise.
-template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false>
+// SK = true compiles the balanced-tail epilogue (parking / reducing shared tiles) in; the other
+// instantiations carry none of its code or registers.
+template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false, bool SK = false>
 __global__ void __launch_bounds__(32 * (2 + NS + kEpiWarps), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
@@ -754,7 +756,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int seg_first = 0, seg_count = 1;          // slots sharing the tile: seg_first .. seg_first + seg_count - 1
             bool reducer = false;
             const int nslots = static_cast<int>(gridDim.x) / CG;
-            if (t.shared) {
+            if (SK && t.shared) {
                 const long long per_tile = p.fold * p.kiters;
                 const long long tile_begin = static_cast<long long>(t.tile - p.sk_first_tile) * per_tile;
                 const long long tile_end = tile_begin + per_tile;
@@ -766,7 +768,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             bool waited_contrib = false, parked = false;
             unsigned int *ticket = nullptr;
-            if (t.shared && seg_count > 1 && row0 < p.M && t.tn * BN + chunk_lo * 32 < p.N) {
+            if (SK && t.shared && seg_count > 1 && row0 < p.M && t.tn * BN + chunk_lo * 32 < p.N) {
                 const size_t region = (static_cast<size_t>(t.tile - p.sk_first_tile) * CG + cta_rank) * kEpiWarps + ew;
                 ticket = p.sk_flags + static_cast<size_t>(gridDim.x) * 2 * kEpiWarps + region;
                 unsigned int old = 0;
@@ -774,12 +776,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 old = __shfl_sync(0xffffffffu, old, 0);
                 reducer = old == static_cast<unsigned int>(seg_count - 1);
             }
-            const bool park_it = t.shared && seg_count > 1 && !reducer;
+            const bool park_it = SK && t.shared && seg_count > 1 && !reducer;
             // The reducer's list of the tile's other units, in slot order: index of their parking place
             // ((cta * 2 + place) * warps + warp, also the index of its ready flag).
             size_t others[kSkMaxShare - 1];
             int n_others = 0, n_before = 0;
-            if (reducer) {
+            if (SK && reducer) {
                 const long long tile_begin = static_cast<long long>(t.tile - p.sk_first_tile) * (p.fold * p.kiters);
                 for (int j = seg_first; j < seg_first + seg_count; ++j) {
                     if (j == unit0) continue;
@@ -809,7 +811,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         parked = true;
                         continue;
                     }
-                    if (reducer) {
+                    if (SK && reducer) {
                         if (!waited_contrib) {
                             // Bounded wait for the ready flag of every other unit of the tile (they took their
                             // tickets earlier, so they are at most one parking pass behind).
@@ -980,7 +982,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     unsigned int *flag = p.sk_flags + ((static_cast<size_t>(my_cta) * 2 + t.park) * kEpiWarps + ew);
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
                 }
-            } else if (reducer) {
+            } else if (SK && reducer) {
                 // every lane has read the parked tiles: ticket and ready flags go back to zero for the next launch
                 __syncwarp();
                 if (lane == 0) {
@@ -1243,11 +1245,10 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     pl.cg = pair_for(pl.bn);
     pl.bk = (pl.bn == 256 && !p.fast_tf32) ? 16 : 32;
     const int bk_env = env_int("MNI_B200_BK", 0);
-    if (bk_env == 16 || bk_env == 32) pl.bk = bk_env;
+    if ((bk_env == 16 || bk_env == 32) && pl.bn == 256) pl.bk = bk_env;   // narrower tiles are built for BK = 32 only
     // Narrow tiles of a lone CTA are bound by shared-memory bandwidth; taking A from tensor memory removes
     // most of A's share of it.
-    pl.ta = !p.fast_tf32 && pl.cg == 1 && pl.bk == 32 && pl.bn <= 128 && env_int("MNI_B200_SPLIT_WARPS", 8) == 8 &&
-            env_int("MNI_B200_TMEM_A", 1) != 0;
+    pl.ta = !p.fast_tf32 && pl.cg == 1 && pl.bk == 32 && pl.bn <= 128 && env_int("MNI_B200_TMEM_A", 1) != 0;
     const size_t raw = static_cast<size_t>(BM + pl.bn / pl.cg) * pl.bk * 4;
     const size_t stage = p.fast_tf32 ? raw : (pl.ta ? raw + static_cast<size_t>(pl.bn) * pl.bk * 4 : 2 * raw);
     const size_t budget = 227 * 1024;
@@ -1300,7 +1301,9 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
             const long long whole = full_rounds > 0 ? full_rounds - 1 : 0;
             const long long range = (tiles - whole * slots) * iters / slots;
             // a tile is shared by at most iters / range + 2 units
-            if (range >= 8 && iters / range + 2 <= kSkMaxShare) {
+            // compiled for the variants that meet ragged waves in practice: 256-wide pairs and narrow tensor-memory tiles
+            const bool built = (pl.cg == 2 && pl.bn == 256) || pl.ta;
+            if (built && range >= 8 && iters / range + 2 <= kSkMaxShare) {
                 pl.sk = true;
                 pl.sk_first_tile = static_cast<int>(whole * slots);
                 pl.grid = static_cast<int>(slots) * pl.cg;
@@ -1315,13 +1318,13 @@ uint32_t desc_hi_bits(uint32_t sbo_bytes, uint32_t layout_type) {
     return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (layout_type << 29);
 }
 
-template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false>
+template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false, bool SK = false>
 cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
                            const CUtensorMap &tmD, const KParams &k, cudaStream_t stream) {
     static std::once_flag once;
     static cudaError_t attr = cudaSuccess;
     std::call_once(once, [] {
-        attr = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FAST, NS, CG, TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        attr = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FAST, NS, CG, TA, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024);
     });
     if (attr != cudaSuccess) return attr;
@@ -1337,7 +1340,7 @@ cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtenso
     attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = CG == 2 ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK, FAST, NS, CG, TA>, tmA, tmB, tmC, tmD, k);
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK, FAST, NS, CG, TA, SK>, tmA, tmB, tmC, tmD, k);
 }
 
 }  // namespace
@@ -1501,25 +1504,30 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     }
 
     cudaError_t e = cudaErrorInvalidValue;
-    const int split_warps = env_int("MNI_B200_SPLIT_WARPS", 8);
-    if (pl.ta && pl.bn == 64) e = launch_variant<64, 32, false, 8, 1, true>(pl, tmA, tmB, tmC, tmD, k, stream);
-    if (pl.ta && pl.bn == 128) e = launch_variant<128, 32, false, 8, 1, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+    if (pl.sk) {
+        if (pl.ta && pl.bn == 64) e = launch_variant<64, 32, false, 8, 1, true, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+        else if (pl.ta && pl.bn == 128) e = launch_variant<128, 32, false, 8, 1, true, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+        else if (!p.fast_tf32 && pl.bk == 16) e = launch_variant<256, 16, false, 8, 2, false, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+        else if (!p.fast_tf32 && pl.bk == 32) e = launch_variant<256, 32, false, 8, 2, false, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+        else if (pl.bk == 16) e = launch_variant<256, 16, true, 4, 2, false, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+        else e = launch_variant<256, 32, true, 4, 2, false, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+    } else if (pl.ta) {
+        if (pl.bn == 64) e = launch_variant<64, 32, false, 8, 1, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+        else e = launch_variant<128, 32, false, 8, 1, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+    }
 #define MNI_VARIANT(BN_, BK_)                                                                         \
     if (pl.cg == 1 && !pl.ta && pl.bn == BN_ && pl.bk == BK_) {                                                 \
         if (p.fast_tf32) e = launch_variant<BN_, BK_, true, 4, 1>(pl, tmA, tmB, tmC, tmD, k, stream);      \
-        else if (split_warps == 8) e = launch_variant<BN_, BK_, false, 8, 1>(pl, tmA, tmB, tmC, tmD, k, stream); \
-        else e = launch_variant<BN_, BK_, false, 4, 1>(pl, tmA, tmB, tmC, tmD, k, stream);                 \
+        else e = launch_variant<BN_, BK_, false, 8, 1>(pl, tmA, tmB, tmC, tmD, k, stream);                 \
     }
 #define MNI_PAIR_VARIANT(BN_, BK_)                                                                    \
-    if (pl.cg == 2 && pl.bn == BN_ && pl.bk == BK_) {                                                 \
+    if (pl.cg == 2 && !pl.sk && pl.bn == BN_ && pl.bk == BK_) {                                                 \
         if (p.fast_tf32) e = launch_variant<BN_, BK_, true, 4, 2>(pl, tmA, tmB, tmC, tmD, k, stream);      \
         else e = launch_variant<BN_, BK_, false, 8, 2>(pl, tmA, tmB, tmC, tmD, k, stream);                 \
     }
-    MNI_PAIR_VARIANT(64, 16) MNI_PAIR_VARIANT(64, 32) MNI_PAIR_VARIANT(128, 16) MNI_PAIR_VARIANT(128, 32)
-    MNI_PAIR_VARIANT(256, 16) MNI_PAIR_VARIANT(256, 32)
+    MNI_PAIR_VARIANT(64, 32) MNI_PAIR_VARIANT(128, 32) MNI_PAIR_VARIANT(256, 16) MNI_PAIR_VARIANT(256, 32)
 #undef MNI_PAIR_VARIANT
-    MNI_VARIANT(64, 16) MNI_VARIANT(64, 32) MNI_VARIANT(128, 16) MNI_VARIANT(128, 32) MNI_VARIANT(256, 16)
-    MNI_VARIANT(256, 32)
+    MNI_VARIANT(64, 32) MNI_VARIANT(128, 32) MNI_VARIANT(256, 16) MNI_VARIANT(256, 32)
 #undef MNI_VARIANT
     if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "gemm_tc_kernel set-up failed: %s", cudaGetErrorString(e));
     MNI_LAUNCH_CHECK("gemm_tc_kernel");
