@@ -76,6 +76,7 @@ struct KParams {
     float *partial;            // split-K: [split][batch][M][N]
     const float *bias;
     int accumulate;
+    int transpose_out;         // the kernel computes C^T (operands exchanged): patches are stored transposed, bias is per row
     int act;                   // 1: also emit gelu(acc + bias) through the second output map
     int store_pre;             // act mode: write the raw product through the first map as well
     unsigned int *err;
@@ -891,18 +892,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         }
                         __syncwarp();
                         if (p.prof) t_wg += clock64() - t_wg0;
-                        uint8_t *dst = my_stage + patch * kEpiBufBytes + lane * 128;
+                        if (p.transpose_out) {
+                            // patch row j = this chunk's column j, float `lane` of it = this lane's row:
+                            // the 32 lanes fill one 128-byte line per store, conflict-free
+                            uint8_t *dst = my_stage + patch * kEpiBufBytes + ((lane & 3) << 2);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            *reinterpret_cast<float4 *>(dst + ((j ^ (lane & 7)) << 4)) =
-                                make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                            __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                            for (int j = 0; j < 32; ++j)
+                                *reinterpret_cast<uint32_t *>(dst + j * 128 + (((lane >> 2) ^ (j & 7)) << 4)) = v[j];
+                        } else {
+                            uint8_t *dst = my_stage + patch * kEpiBufBytes + lane * 128;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *reinterpret_cast<float4 *>(dst + ((j ^ (lane & 7)) << 4)) =
+                                    make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                        }
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
                         if (lane == 0) {
                             const uint32_t src = smem_u32(my_stage + patch * kEpiBufBytes);
-                            if (reduce) tma_reduce_add_5d(map, src, col0, row0, cbatch);
-                            else tma_store_5d(map, src, col0, row0, cbatch);
+                            const int c0 = p.transpose_out ? row0 : col0, c1 = p.transpose_out ? col0 : row0;
+                            if (reduce) tma_reduce_add_5d(map, src, c0, c1, cbatch);
+                            else tma_store_5d(map, src, c0, c1, cbatch);
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                             ++in_flight;
                         }
@@ -910,7 +921,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     };
                     const bool do_act = fuse && p.act != 0;          // host guarantees use_tma in this mode
                     if (do_act && p.store_pre) emit(&tmC, false);    // the raw product, what the tape saves
-                    if (fuse && p.bias != nullptr) {
+                    if (fuse && p.bias != nullptr && p.transpose_out) {
+                        const float b = row0 + lane < p.M ? __ldg(p.bias + row0 + lane) : 0.f;   // one bias value per row here
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
+                    } else if (fuse && p.bias != nullptr) {
                         if (bias_vec && col0 + 32 <= p.N) {
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
@@ -1391,6 +1406,21 @@ int read_role_waits(uint64_t out[8], int reset) {
     return MNI_B200_OK;
 }
 
+// The kernel's view of a problem.  An output with few rows and many columns would fill at most half of
+// every 128-row MMA; with the operands exchanged the kernel computes C^T in 64-wide tiles instead and its
+// epilogue stores the 32 x 32 patches transposed, so C is written in place as before.
+GemmProblem kernel_view(const GemmProblem &p, bool *transposed) {
+    *transposed = false;
+    const bool storable = (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && p.ldc % 4 == 0 && p.c_bstride % 4 == 0 &&
+                          p.N % 4 == 0 && env_int("MNI_B200_NO_TMA_STORE", 0) == 0 && env_int("MNI_B200_EPI_VECTOR", 0) == 0;
+    if (p.D != nullptr || p.M > 64 || p.N < 256 || !storable || env_int("MNI_B200_TRANSPOSE_OUT", 1) == 0) return p;
+    GemmProblem q = p;
+    std::swap(q.A, q.B);
+    std::swap(q.M, q.N);
+    *transposed = true;
+    return q;
+}
+
 bool gemm_tc_can_fuse_activation(const GemmProblem &p, int sm_count) {
     const Plan pl = make_plan(p, sm_count);
     auto aligned = [&](const float *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
@@ -1398,16 +1428,21 @@ bool gemm_tc_can_fuse_activation(const GemmProblem &p, int sm_count) {
            env_int("MNI_B200_NO_TMA_STORE", 0) == 0 && env_int("MNI_B200_EPI_VECTOR", 0) == 0;
 }
 
-size_t gemm_tc_partial_bytes(const GemmProblem &p, int sm_count) {
+size_t gemm_tc_partial_bytes(const GemmProblem &p0, int sm_count) {
+    bool transposed = false;
+    const GemmProblem p = kernel_view(p0, &transposed);
     const Plan pl = make_plan(p, sm_count);
     if (pl.sk) return static_cast<size_t>(pl.grid) * 2 * BM * pl.bn * sizeof(float);   // two parked accumulators per CTA
     if (pl.splits <= 1) return 0;
     return static_cast<size_t>(pl.splits) * p.batch * p.M * p.N * sizeof(float);
 }
 
-int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int sm_count,
+int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, int sm_count,
                    cudaStream_t stream) {
-    if (p.M <= 0 || p.N <= 0 || p.batch <= 0) return MNI_B200_OK;
+    if (p0.M <= 0 || p0.N <= 0 || p0.batch <= 0) return MNI_B200_OK;
+    bool transposed = false;
+    const GemmProblem p = kernel_view(p0, &transposed);       // p.M / p.N are the kernel's; oM / oN the output's
+    const int64_t oM = p0.M, oN = p0.N;
     const Plan pl = make_plan(p, sm_count);
     if (p.K <= 0) return fail(MNI_B200_ERR_ARG, "empty contraction reached the tensor-core launcher");
     if ((pl.splits > 1 || pl.sk) && partial == nullptr)
@@ -1424,7 +1459,7 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
 
     // Epilogue: TMA store when the destination rows are 16-byte aligned, plain stores otherwise.
     float *dst = pl.splits > 1 ? partial : p.C;
-    const int64_t dst_ld = pl.splits > 1 ? p.N : p.ldc;
+    const int64_t dst_ld = pl.splits > 1 ? oN : p.ldc;
     const int64_t dst_bs = pl.splits > 1 ? p.M * p.N : p.c_bstride;
     const int64_t dst_batches = pl.splits > 1 ? static_cast<int64_t>(pl.splits) * p.batch : p.batch;
     const bool tma_ok = (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && dst_ld % 4 == 0 && dst_bs % 4 == 0 &&
@@ -1436,7 +1471,7 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
         tmC = tmA;
     } else if (tma_ok && (dst != nullptr || p.D != nullptr)) {
         if (dst != nullptr) {
-            rc = make_output_map(&tmC, dst, p.N, p.M, dst_batches, dst_ld, dst_bs);
+            rc = make_output_map(&tmC, dst, oN, oM, dst_batches, dst_ld, dst_bs);
             if (rc) return rc;
         } else {
             tmC = tmA;
@@ -1455,6 +1490,7 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
 
     k.M = static_cast<int>(p.M);
     k.N = static_cast<int>(p.N);
+    k.transpose_out = transposed ? 1 : 0;
     k.tiles_m = pl.tiles_m;
     k.tiles_n = pl.tiles_n;
     k.group_m = std::max(1, std::min(pl.tiles_m, env_int("MNI_B200_GROUP_M", 16)));
@@ -1532,16 +1568,16 @@ int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int
     if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "gemm_tc_kernel set-up failed: %s", cudaGetErrorString(e));
     MNI_LAUNCH_CHECK("gemm_tc_kernel");
     if (pl.splits > 1) {
-        const long long rows = static_cast<long long>(p.batch) * p.M;
-        const bool vec = p.N % 4 == 0 && p.ldc % 4 == 0 && p.c_bstride % 4 == 0 &&
+        const long long rows = static_cast<long long>(p.batch) * oM;
+        const bool vec = oN % 4 == 0 && p.ldc % 4 == 0 && p.c_bstride % 4 == 0 &&
                          ((reinterpret_cast<uintptr_t>(p.C) | reinterpret_cast<uintptr_t>(partial) |
                            reinterpret_cast<uintptr_t>(p.bias)) & 15) == 0;
-        const long long items = rows * (vec ? p.N / 4 : p.N);
+        const long long items = rows * (vec ? oN / 4 : oN);
         const unsigned blocks = static_cast<unsigned>((items + 255) / 256);
         const bool small = items < (1LL << 31) - 256;
 #define MNI_REDUCE(V_, I_)                                                                                          \
     splitk_reduce_kernel<V_, I_><<<blocks, 256, 0, stream>>>(partial, p.C, p.ldc, p.c_bstride, p.bias, p.accumulate, \
-                                                             pl.splits, rows, k.M, k.N)
+                                                             pl.splits, rows, static_cast<int>(oM), static_cast<int>(oN))
         if (vec && small) MNI_REDUCE(float4, unsigned);
         else if (vec) MNI_REDUCE(float4, long long);
         else if (small) MNI_REDUCE(float, unsigned);

@@ -436,3 +436,32 @@ def test_balanced_tail_is_reproducible_and_leaves_flags_clear(F, monkeypatch):
     monkeypatch.setenv("MNI_B200_STREAMK", "0")
     whole = F.matmul(a, b).numpy()
     assert rel_fro(first, whole) < 1e-5          # two summation orders of 3xTF32 products
+
+
+@pytest.mark.parametrize("m,k,n,batch", [(40, 300, 512, ()), (64, 512, 512, (3,)), (16, 1024, 2048, ()), (33, 96, 260, (2, 2))])
+def test_few_rows_many_columns_is_computed_transposed(F, oracle, m, k, n, batch):
+    """M <= 64 with N >= 256: the kernel computes C^T with the operands exchanged and stores transposed patches
+    (bias then runs along the kernel's rows).  Forward with bias, accumulate, a forced K split and both
+    gradients against the CPU backend."""
+    rng = np.random.default_rng(m * 1000 + n)
+    a = rng.standard_normal(batch + (m, k), dtype=np.float32)
+    b = rng.standard_normal(batch + (k, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    H = oracle.HostTensor
+    ref = oracle.matmul(H.from_array(a), H.from_array(b)).numpy()
+    ad, bd, biasd = (F.DeviceTensor.from_numpy(x) for x in (a, b, bias))
+    tol = tol_3xtf32(k, a, b) + 1e-5
+    for flags in (F._lib.FORCE_TENSOR_PATH, F._lib.FORCE_TENSOR_PATH | (3 << 16)):
+        out = F.matmul(ad, bd, biasd, flags=flags)
+        F.device_status()
+        assert float(np.max(np.abs(out.numpy() - (ref + bias)))) <= tol, hex(flags)
+    base = rng.standard_normal(ref.shape, dtype=np.float32)
+    out = F.DeviceTensor.from_numpy(base)
+    F.matmul(ad, bd, out=out, flags=F._lib.FORCE_TENSOR_PATH | F._lib.ACCUMULATE_C)
+    assert float(np.max(np.abs(out.numpy() - (base + ref)))) <= tol
+    g = rng.standard_normal(ref.shape, dtype=np.float32)
+    da, db = F.matmul_backward(F.DeviceTensor.from_numpy(g), ad, bd, flags=F._lib.FORCE_TENSOR_PATH)
+    F.device_status()
+    ra, rb = oracle.matmul_backward(H.from_array(g), H.from_array(a), H.from_array(b))
+    assert float(np.max(np.abs(da.numpy() - ra.numpy()))) <= tol_3xtf32(n, g, b)
+    assert float(np.max(np.abs(db.numpy() - rb.numpy()))) <= tol_3xtf32(m, a, g)
