@@ -235,7 +235,9 @@ skinny_dw_kernel(const float *__restrict__ x, long long ldx, const float *__rest
 // L1/L2) and a shuffle tree folds the 32 lane sums.  W is read exactly once.
 constexpr int kDxThreads = 256;
 constexpr int kDxRows = 2;
-template <int MT>
+// FULL: M == MT and N a multiple of 512, so the loop carries no bounds tests and the compiler can issue
+// all 8 weight loads and all 4 * MT dy loads of a step before the first multiply.
+template <int MT, bool FULL>
 __global__ void __launch_bounds__(kDxThreads)
 skinny_dx_kernel(const float *__restrict__ dy, long long lddy, const float *__restrict__ W, long long ldw,
                  float *__restrict__ dx, long long lddx, int accumulate, int M, long long N, long long K) {
@@ -259,7 +261,7 @@ skinny_dx_kernel(const float *__restrict__ dy, long long lddy, const float *__re
 #pragma unroll
         for (int q = 0; q < P; ++q) {
             const long long nq = n + 128 * q;
-            if (nq < N) {
+            if (FULL || nq < N) {
                 wa[q] = __ldcs(reinterpret_cast<const float4 *>(w0 + nq));
                 wb[q] = __ldcs(reinterpret_cast<const float4 *>(w1 + nq));
             } else {
@@ -269,11 +271,11 @@ skinny_dx_kernel(const float *__restrict__ dy, long long lddy, const float *__re
         }
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
-            if (m < M) {
+            if (FULL || m < M) {
 #pragma unroll
                 for (int q = 0; q < P; ++q) {
                     const long long nq = n + 128 * q;
-                    if (nq < N) {
+                    if (FULL || nq < N) {
                         const float4 g = __ldg(reinterpret_cast<const float4 *>(dy + m * lddy + nq));
                         acc[0][m] = fmaf(g.x, wa[q].x, fmaf(g.y, wa[q].y, fmaf(g.z, wa[q].z, fmaf(g.w, wa[q].w, acc[0][m]))));
                         acc[1][m] = fmaf(g.x, wb[q].x, fmaf(g.y, wb[q].y, fmaf(g.z, wb[q].z, fmaf(g.w, wb[q].w, acc[1][m]))));
@@ -365,10 +367,15 @@ int launch_skinny_dx(const float *dy, int64_t lddy, const float *W, int64_t ldw,
     const int mt = pick_mt(M);
     const long long rows_per_block = (kDxThreads / 32) * kDxRows;
     const unsigned blocks = static_cast<unsigned>((K + rows_per_block - 1) / rows_per_block);
+    const bool full = M == mt && mt >= 4 && N % 512 == 0;   // measured: slower than the guarded loop for 1-2 rows
 #define MNI_SKINNY_DX(MT)                                                                              \
     case MT:                                                                                           \
-        skinny_dx_kernel<MT><<<blocks, kDxThreads, 0, stream>>>(dy, lddy, W, ldw, dx, lddx, accumulate ? 1 : 0, \
-                                                                (int)M, N, K);                         \
+        if (full)                                                                                      \
+            skinny_dx_kernel<MT, true><<<blocks, kDxThreads, 0, stream>>>(dy, lddy, W, ldw, dx, lddx,    \
+                                                                           accumulate ? 1 : 0, (int)M, N, K); \
+        else                                                                                           \
+            skinny_dx_kernel<MT, false><<<blocks, kDxThreads, 0, stream>>>(dy, lddy, W, ldw, dx, lddx,   \
+                                                                            accumulate ? 1 : 0, (int)M, N, K); \
         break;
     switch (mt) {
         MNI_SKINNY_DX(1) MNI_SKINNY_DX(2) MNI_SKINNY_DX(4) MNI_SKINNY_DX(8)
