@@ -186,19 +186,60 @@ class Problem:
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clock, power and clock-event (throttle) reasons while the timed region runs.
+
+    NVML is read directly from a thread every 2 ms (a timed region can be shorter than one `nvidia-smi -lms`
+    period); `nvidia-smi` in a subprocess is the fallback when the NVML binding is missing.  Read-only queries.
+    """
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
     def __init__(self, gpu_index: int):
         self.gpu_index, self.proc, self.lines = gpu_index, None, []
+        self.samples, self.smax, self._stop, self._thread, self.source = [], None, False, None, None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        index = self.gpu_index
+        if visible:
+            entry = visible.split(",")[self.gpu_index].strip()
+            if entry.isdigit():
+                index = int(entry)
+            else:
+                return pynvml, pynvml.nvmlDeviceGetHandleByUUID(entry)
+        return pynvml, pynvml.nvmlDeviceGetHandleByIndex(index)
 
     def start(self):
+        try:
+            nv, handle = self._nvml_handle()
+            self.smax = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                nv.nvmlDeviceGetCurrentClocksThrottleReasons
+
+            def loop():
+                while not self._stop:
+                    try:
+                        self.samples.append((time.time(), float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)),
+                                             nv.nvmlDeviceGetPowerUsage(handle) / 1000.0, int(reasons_fn(handle))))
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+
+            self.source = "nvml"
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self.source = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                  "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.source = "nvidia-smi"
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
@@ -208,6 +249,19 @@ class ClockSampler:
             self.lines.append((time.time(), line.strip()))
 
     def stop(self, t0: float, t1: float) -> dict:
+        if self.source == "nvml":
+            self._stop = True
+            self._thread.join(timeout=1.0)
+            rows = [r for r in self.samples if t0 <= r[0] <= t1] or self.samples[-3:]
+            sm = [r[1] for r in rows]
+            power = [r[2] for r in rows]
+            mask = 0
+            for r in rows:
+                mask |= r[3]
+            reasons = sorted(name for bit, name in self.REASON_BITS.items() if mask & bit)
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_min_mhz": min(sm) if sm else None,
+                    "sm_max_mhz": self.smax, "power_w_max": max(power) if power else None, "reasons": reasons,
+                    "samples": len(sm), "source": "nvml, 2 ms period, timed region only"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.1)
@@ -228,7 +282,8 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax,
-                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm),
+                "source": "nvidia-smi -lms 50"}
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -342,6 +397,25 @@ def run_ours(args):
     ms_per_step = total_ms / args.steps
     value = wl.flops * world / (ms_per_step * 1e-3) / 1e12
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    # NVML refreshes its clock and throttle readings far more slowly than a timed region of ~0.1 s lasts, so
+    # the same steps are repeated, untimed, for about a second with a second sampler: what the clocks settle
+    # at under this workload, reported beside the readings taken during the timed region.
+    sustain_steps = int(min(20000, max(args.steps, 1000.0 / max(ms_per_step, 1e-3))))
+    sustain = ClockSampler(local_rank)
+    if rank == 0:
+        sustain.start()
+    t_s0 = time.time()
+    sustain_ms = timed(step, sustain_steps, after=join_comm)
+    t_s1 = time.time()
+    if rank == 0:
+        settled = sustain.stop(t_s0 + 0.5 * (t_s1 - t_s0), t_s1)       # second half of the window
+        clocks["sustained"] = {"seconds": round(t_s1 - t_s0, 2), "steps": sustain_steps,
+                               "ms_per_step": sustain_ms / sustain_steps, "sm_mhz": settled.get("sm_mhz"),
+                               "sm_min_mhz": settled.get("sm_min_mhz"), "power_w_max": settled.get("power_w_max"),
+                               "reasons": settled.get("reasons"), "samples": settled.get("samples")}
+        for r in settled.get("reasons") or []:
+            if r not in clocks["reasons"]:
+                clocks["reasons"].append(r)
 
     # ---- roofline of the dominant kernel: the forward launch(es) timed alone ----
     peaks = {}
