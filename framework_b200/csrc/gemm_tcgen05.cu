@@ -448,6 +448,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int unit0 = static_cast<int>(blockIdx.x) / CG;           // this CTA (pair) starts at this unit ...
     const int unit_step = static_cast<int>(gridDim.x) / CG;        // ... and strides by the number of CTAs (pairs)
 
+    if (warp == 0 && lane == 1) {
+        // descriptor fetches overlap the barrier and TMEM set-up
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmB)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmC)) : "memory");
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(bar_full + 8u * s, 1);
@@ -1014,7 +1020,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             ++acc_it;
         }
-        if (use_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        // The staging patches must have been read before the CTA gives up its shared memory; the global
+        // writes themselves complete with the grid like any other store.
+        if (use_tma && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         if (p.prof && warp == 2 + NS && lane == 0) {
             atomicAdd(p.prof + 4, static_cast<unsigned long long>(waited));
             atomicAdd(p.prof + 7, static_cast<unsigned long long>(t_wg));
