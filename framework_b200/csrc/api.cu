@@ -599,6 +599,11 @@ int with_scratch(uint32_t flags, void *stream, Body body) {
 
 }  // namespace
 
+bool pdl_enabled() {
+    static const bool on = env_flag("MNI_B200_PDL", 1);
+    return on;
+}
+
 int fail(int status, const char *fmt, ...) {
     va_list ap;
     va_start(ap, fmt);

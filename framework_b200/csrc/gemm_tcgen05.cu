@@ -448,6 +448,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int unit0 = static_cast<int>(blockIdx.x) / CG;           // this CTA (pair) starts at this unit ...
     const int unit_step = static_cast<int>(gridDim.x) / CG;        // ... and strides by the number of CTAs (pairs)
 
+    if (threadIdx.x == 0) grid_dependency_trigger();    // the next grid in the stream may be scheduled already
     if (warp == 0 && lane == 1) {
         // descriptor fetches overlap the barrier and TMEM set-up
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
@@ -488,6 +489,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if constexpr (CG == 2) cluster_sync_all();   // the peer's barriers exist before anyone arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dependency_wait();      // everything above overlapped the previous grid; its results are needed from here on
 
 
     if (warp == 0) {
@@ -1057,6 +1059,8 @@ __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float *__restrict__ partial, float *__restrict__ C, long long ldc, long long c_bstride,
                      const float *__restrict__ bias, int accumulate, int splits, long long rows, int M, int N) {
     constexpr int W = sizeof(V) / sizeof(float);
+    grid_dependency_trigger();
+    grid_dependency_wait();                      // the partials come from the grid before this one
     const I per_row = static_cast<I>(N / W);
     const I item = static_cast<I>(blockIdx.x) * 256 + threadIdx.x;
     if (item >= static_cast<I>(rows) * per_row) return;
@@ -1356,13 +1360,15 @@ cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtenso
     cfg.blockDim = dim3(32 * (2 + NS + kEpiWarps));
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attrs[1];
-    attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = CG;
-    attrs[0].val.clusterDim.y = 1;
-    attrs[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    attrs[1].id = cudaLaunchAttributeClusterDimension;
+    attrs[1].val.clusterDim.x = CG;
+    attrs[1].val.clusterDim.y = 1;
+    attrs[1].val.clusterDim.z = 1;
     cfg.attrs = attrs;
-    cfg.numAttrs = CG == 2 ? 1 : 0;
+    cfg.numAttrs = CG == 2 ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK, FAST, NS, CG, TA, SK>, tmA, tmB, tmC, tmD, k);
 }
 
@@ -1584,13 +1590,15 @@ int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, in
         const unsigned blocks = static_cast<unsigned>((items + 255) / 256);
         const bool small = items < (1LL << 31) - 256;
 #define MNI_REDUCE(V_, I_)                                                                                          \
-    splitk_reduce_kernel<V_, I_><<<blocks, 256, 0, stream>>>(partial, p.C, p.ldc, p.c_bstride, p.bias, p.accumulate, \
-                                                             pl.splits, rows, static_cast<int>(oM), static_cast<int>(oN))
+    e = launch_dependent(splitk_reduce_kernel<V_, I_>, dim3(blocks), dim3(256), 0, stream, partial, p.C, p.ldc,        \
+                         p.c_bstride, p.bias, p.accumulate ? 1 : 0, pl.splits, rows, static_cast<int>(oM),          \
+                         static_cast<int>(oN))
         if (vec && small) MNI_REDUCE(float4, unsigned);
         else if (vec) MNI_REDUCE(float4, long long);
         else if (small) MNI_REDUCE(float, unsigned);
         else MNI_REDUCE(float, long long);
 #undef MNI_REDUCE
+        if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "splitk_reduce_kernel launch failed: %s", cudaGetErrorString(e));
         MNI_LAUNCH_CHECK("splitk_reduce_kernel");
     }
     return MNI_B200_OK;

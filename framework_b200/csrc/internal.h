@@ -15,6 +15,38 @@
 namespace mni {
 
 // ---------------------------------------------------------------------------
+// programmatic dependent launch
+// ---------------------------------------------------------------------------
+// Short kernels that follow one another in a stream (GEMM -> split-K finish -> GEMM, the three skinny
+// products of a step) are launched with programmatic stream serialization: the next grid may be scheduled,
+// and run its set-up, while its predecessor still runs; before it touches global memory it executes
+// griddepcontrol.wait, which returns once the predecessor has completed and its writes are visible.
+// MNI_B200_PDL=0 turns the attribute off (the device-side instructions are then no-ops).
+bool pdl_enabled();
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_trigger() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
+// ---------------------------------------------------------------------------
 // error plumbing
 // ---------------------------------------------------------------------------
 int fail(int status, const char *fmt, ...);          // records the thread-local message, returns status
