@@ -452,8 +452,32 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
     const bool acc_dbias = (c.flags & MNI_B200_ACCUMULATE_DBIAS) != 0;
     const int64_t a_elems = s.a_batch * s.M * s.K, b_elems = s.b_batch * s.K * s.N;
 
+    // The two gradient products of a small problem each fill only part of the GPU, a skinny one's are short,
+    // launch-bound kernels, and a medium one's leave a ragged last wave: issue grad_b on the side stream next
+    // to grad_a and join before returning.  The column sums of the bias gradient are HBM-bound and always go
+    // to the side stream, where they run beside the tensor-bound products instead of in front of them.
+    const double work = static_cast<double>(s.M) * static_cast<double>(s.N) * static_cast<double>(s.K) *
+                        static_cast<double>(std::max<int64_t>(g_batch, 1));
+    const bool side_on = !c.dry() && env_flag("MNI_B200_BWD_OVERLAP", 1);
+    const bool overlap = side_on && da && db && a_elems > 0 && b_elems > 0 && work > 0 && work <= overlap_work_limit();
+    const bool side_dbias = side_on && dbias && (da || db) && work > 0;
+    cudaStream_t const main_stream = c.stream;
+    if (overlap || side_dbias) {
+        MNI_CUDA(cudaEventRecord(c.st->ev_fork, main_stream));
+        MNI_CUDA(cudaStreamWaitEvent(c.st->side, c.st->ev_fork, 0));
+    }
+    struct Join {      // joins the side stream on every exit path once it has been forked
+        Call &c; cudaStream_t main; bool on;
+        ~Join() {
+            if (!on) return;
+            c.stream = main;
+            if (cudaEventRecord(c.st->ev_join, c.st->side) == cudaSuccess) cudaStreamWaitEvent(main, c.st->ev_join, 0);
+        }
+    } join{c, main_stream, overlap || side_dbias};
+
     if (dbias) {
         // Column sums over every row of dc (ops/elementwise.rs:224-229 via utils::unbroadcast).
+        if (side_dbias) c.stream = c.st->side;
         const int64_t rows = g_batch * s.M;
         if (rows == 0 || s.N == 0) {
             rc = zero_or_bias_fill(c, dbias, 1, s.N, nullptr, acc_dbias);
@@ -486,26 +510,7 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
         }
     }
 
-    // The two gradient products of a small problem each fill only part of the GPU, a skinny one's are short,
-    // launch-bound kernels, and a medium one's leave a ragged last wave: issue grad_b on the side stream next
-    // to grad_a and join before returning.
-    const double work = static_cast<double>(s.M) * static_cast<double>(s.N) * static_cast<double>(s.K) *
-                        static_cast<double>(std::max<int64_t>(g_batch, 1));
-    const bool overlap = !c.dry() && da && db && a_elems > 0 && b_elems > 0 && work > 0 && work <= overlap_work_limit() &&
-                         env_flag("MNI_B200_BWD_OVERLAP", 1);
-    cudaStream_t const main_stream = c.stream;
-    if (overlap) {
-        MNI_CUDA(cudaEventRecord(c.st->ev_fork, main_stream));
-        MNI_CUDA(cudaStreamWaitEvent(c.st->side, c.st->ev_fork, 0));
-    }
-    struct Join {      // joins the side stream on every exit path once it has been forked
-        Call &c; cudaStream_t main; bool on;
-        ~Join() {
-            if (!on) return;
-            c.stream = main;
-            if (cudaEventRecord(c.st->ev_join, c.st->side) == cudaSuccess) cudaStreamWaitEvent(main, c.st->ev_join, 0);
-        }
-    } join{c, main_stream, overlap};
+    c.stream = main_stream;
 
     // grad_a = unbroadcast(dc . b^T, a.shape)   (ops/matmul.rs:231-240)
     if (da && a_elems > 0) {

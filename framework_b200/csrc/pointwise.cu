@@ -46,7 +46,18 @@ __global__ void colsum_partial_kernel(const float *__restrict__ dy, long long ld
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     const bool vec = ((ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(dy) & 15) == 0) && col + 3 < n;
     if (col < n) {
-        for (long long r = r0 + warp; r < r1; r += 8) {
+        long long r = r0 + warp;
+        if (vec) {
+            // four rows in flight per thread, added in the same ascending order as the one-row loop
+            for (; r + 24 < r1; r += 32) {
+                float4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = __ldcs(reinterpret_cast<const float4 *>(dy + (r + 8 * u) * ld + col));
+#pragma unroll
+                for (int u = 0; u < 4; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+            }
+        }
+        for (; r < r1; r += 8) {
             const float *p = dy + r * ld + col;
             if (vec) {
                 const float4 v = __ldg(reinterpret_cast<const float4 *>(p));
