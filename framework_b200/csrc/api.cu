@@ -49,6 +49,11 @@ double overlap_work_limit() {
     return v && *v ? atof(v) : 4.0e9;   // measured: helps up to the attention-shaped products (1.6e9), neutral beyond
 }
 
+// Row counts up to which the streaming kernels beat the tensor path (measured at K = N = 4096 with a weight
+// that is not in L2: forward 16.5-19.2 vs 23.7 us up to 4 rows and 26.7 vs 23.7 from 5; dx 19.4 vs 23.6 at 5
+// rows and 31.0 vs 23.7 at 8; dW 13.5 vs 16.9 at 8 rows and 21.8 vs 17.0 at 12).
+constexpr int64_t kSkinnyFwdRows = 4, kSkinnyDxRows = 5, kSkinnyDwRows = 8;
+
 bool env_flag(const char *name, int dflt) {
     const char *v = getenv(name);
     return (v && *v ? atoi(v) : dflt) != 0;
@@ -311,7 +316,7 @@ int fwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, float *out
     if (s.K == 0) return zero_or_bias_fill(c, out, s.batch * s.M, s.N, bias, accumulate);
 
     const bool want_skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
-                             ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 8);
+                             ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= kSkinnyFwdRows);
     if (want_skinny && s.batch == 1 && skinny_fwd_supported(s.M, s.N, s.K)) {
         const int an = a->ndim, bn = b->ndim;
         const bool a_ok = a->stride[an - 1] == 1 || s.K == 1;
@@ -357,7 +362,7 @@ int fwd_gelu_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const
     const uint32_t saved_flags = c.flags;
     c.flags &= ~static_cast<uint32_t>(MNI_B200_ACCUMULATE_C);
     const bool skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
-                        ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 8);
+                        ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= kSkinnyFwdRows);
     if (s.K > 0 && !skinny) {
         GemmProblem p;
         rc = make_operand(c, *a, false, p.A);
@@ -519,7 +524,7 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
             if (rc) return rc;
         } else {
             const bool skinny_dx = ((c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
-                                    ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 8)) &&
+                                    ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= kSkinnyDxRows)) &&
                                    s.batch == 1 && g_batch == 1 && s.a_batch == 1 && s.b_batch == 1 &&
                                    dc->stride[gn - 1] == 1 && b->stride[b->ndim - 1] == 1 && s.K > 1 &&
                                    skinny_dx_supported(dc->ptr, dc->stride[gn - 2], b->ptr, b->stride[b->ndim - 2], s.M, s.N);
@@ -554,7 +559,7 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
             if (rc) return rc;
         } else {
             const bool want_skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
-                                     ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= 8);
+                                     ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= kSkinnyDwRows);
             const bool plain2d = s.batch == 1 && g_batch == 1 && s.M <= 16;
             if (want_skinny && plain2d && (a->stride[a->ndim - 1] == 1 || s.K == 1) &&
                 (dc->stride[gn - 1] == 1 || s.N == 1)) {
