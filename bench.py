@@ -397,26 +397,6 @@ def run_ours(args):
     ms_per_step = total_ms / args.steps
     value = wl.flops * world / (ms_per_step * 1e-3) / 1e12
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
-    # NVML refreshes its clock and throttle readings far more slowly than a timed region of ~0.1 s lasts, so
-    # the same steps are repeated, untimed, for about a second with a second sampler: what the clocks settle
-    # at under this workload, reported beside the readings taken during the timed region.
-    sustain_steps = int(min(20000, max(args.steps, 1000.0 / max(ms_per_step, 1e-3))))
-    sustain = ClockSampler(local_rank)
-    if rank == 0:
-        sustain.start()
-    t_s0 = time.time()
-    sustain_ms = timed(step, sustain_steps, after=join_comm)
-    t_s1 = time.time()
-    if rank == 0:
-        settled = sustain.stop(t_s0 + 0.5 * (t_s1 - t_s0), t_s1)       # second half of the window
-        clocks["sustained"] = {"seconds": round(t_s1 - t_s0, 2), "steps": sustain_steps,
-                               "ms_per_step": sustain_ms / sustain_steps, "sm_mhz": settled.get("sm_mhz"),
-                               "sm_min_mhz": settled.get("sm_min_mhz"), "power_w_max": settled.get("power_w_max"),
-                               "reasons": settled.get("reasons"), "samples": settled.get("samples")}
-        for r in settled.get("reasons") or []:
-            if r not in clocks["reasons"]:
-                clocks["reasons"].append(r)
-
     # ---- roofline of the dominant kernel: the forward launch(es) timed alone ----
     peaks = {}
     try:
@@ -505,6 +485,26 @@ def run_ours(args):
     e2e_ms = timed(e2e_step, e2e_steps, after=e2e_join) / e2e_steps
     e2e_value = wl.flops * world / (e2e_ms * 1e-3) / 1e12
     F.device_status()
+
+    # Last measurement of the run (it heats the GPU to its power cap).  NVML refreshes its clock and throttle readings far more slowly than a timed region of ~0.1 s lasts, so
+    # the same steps are repeated, untimed, for about a second with a second sampler: what the clocks settle
+    # at under this workload, reported beside the readings taken during the timed region.
+    sustain_steps = int(min(20000, max(args.steps, 1000.0 / max(ms_per_step, 1e-3))))
+    sustain = ClockSampler(local_rank)
+    if rank == 0:
+        sustain.start()
+    t_s0 = time.time()
+    sustain_ms = timed(step, sustain_steps, after=join_comm)
+    t_s1 = time.time()
+    if rank == 0:
+        settled = sustain.stop(t_s0 + 0.5 * (t_s1 - t_s0), t_s1)       # second half of the window
+        clocks["sustained"] = {"seconds": round(t_s1 - t_s0, 2), "steps": sustain_steps,
+                               "ms_per_step": sustain_ms / sustain_steps, "sm_mhz": settled.get("sm_mhz"),
+                               "sm_min_mhz": settled.get("sm_min_mhz"), "power_w_max": settled.get("power_w_max"),
+                               "reasons": settled.get("reasons"), "samples": settled.get("samples")}
+        for r in settled.get("reasons") or []:
+            if r not in clocks["reasons"]:
+                clocks["reasons"].append(r)
 
     if rank == 0:
         cpu = cpu_baseline_sample(base, threads=1) if (world == 1 and not args.no_cpu) else None
