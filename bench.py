@@ -121,7 +121,7 @@ WORKLOADS = {
 HBM_BOUND = ("c3", "c5b1", "c5b4", "c5b16")
 # DRAM bytes per forward launch from ncu captures of the same launch
 # (dram__bytes_read.sum + dram__bytes_write.sum; 3xTF32 build with CTA pairs).
-NCU_TRAFFIC_BYTES = {"c2": 34.25e6 + 19.98e6}
+NCU_TRAFFIC_BYTES = {"c2": 34.11e6 + 19.63e6}
 
 
 def shard_workload(wl: Workload, rank: int, world: int) -> Workload:
