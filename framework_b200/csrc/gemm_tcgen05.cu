@@ -54,6 +54,28 @@ constexpr long long kWaitCycles = 4000000000LL;            // ~2 s at 2 GHz
 enum OperandMode { kKMajor = 0, kMnMultiBox = 1, kMnSingleBox = 2 };
 enum EpilogueMode { kEpiPlainStores = 0, kEpiTmaStore = 1, kEpiTmaReduce = 2, kEpiVectorStores = 3 };
 
+// Division by a launch-time constant as a multiply-high and a shift (exact for 0 <= n < 2^31): every role
+// decodes every tile it visits, and with short contractions a handful of hardware divisions per tile showed
+// up as 1 250 cycles of a 3 000-cycle main loop.  mul = ceil(2^(31 + ceil(log2 d)) / d), shr = ceil(log2 d) - 1.
+struct FastDiv {
+    uint32_t mul, shr, d;
+};
+__host__ inline FastDiv make_fastdiv(long long d_in) {
+    FastDiv f;
+    const uint32_t d = static_cast<uint32_t>(d_in < 1 ? 1 : d_in);
+    f.d = d;
+    if (d == 1) { f.mul = 0; f.shr = 0; return f; }
+    uint32_t l = 0;
+    while ((1ull << l) < d) ++l;
+    const uint32_t p = 31 + l;
+    f.mul = static_cast<uint32_t>(((1ull << p) + d - 1) / d);
+    f.shr = p - 32;
+    return f;
+}
+__device__ __forceinline__ int fd_div(int n, const FastDiv &f) {
+    return f.d == 1 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), f.mul) >> f.shr);
+}
+
 struct KParams {
     int M, N;
     int tiles_m, tiles_n, group_m;
@@ -79,6 +101,8 @@ struct KParams {
     int transpose_out;         // the kernel computes C^T (operands exchanged): patches are stored transposed, bias is per row
     int act;                   // 1: also emit gelu(acc + bias) through the second output map
     int store_pre;             // act mode: write the raw product through the first map as well
+    FastDiv fd_splits, fd_per_batch, fd_group_sz, fd_group_m, fd_last_gm;   // decode_unit
+    FastDiv fd_a_cnt, fd_a_d1, fd_a_d2, fd_b_cnt, fd_b_d1, fd_b_d2;         // batch_coords
     unsigned int *err;
     unsigned long long *prof;  // optional role wait counters (null = off)
     // Balanced tail ("stream-K"): tiles [sk_first_tile, tiles) are not dealt out whole; their k-blocks are
@@ -306,20 +330,20 @@ struct TileCoord {
 
 __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit) {
     TileCoord t;
-    const int tile = unit / p.splits;
+    const int tile = fd_div(unit, p.fd_splits);
     t.split = unit - tile * p.splits;
     t.shared = 0;
     t.park = 0;
     t.tile = tile;
     const int per_batch = p.tiles_m * p.tiles_n;
-    t.bt = tile / per_batch;
+    t.bt = fd_div(tile, p.fd_per_batch);
     const int r = tile - t.bt * per_batch;
     const int group_sz = p.group_m * p.tiles_n;
-    const int g = r / group_sz;
+    const int g = fd_div(r, p.fd_group_sz);
     const int first_m = g * p.group_m;
-    const int gm = min(p.group_m, p.tiles_m - first_m);
+    const int gm = min(p.group_m, p.tiles_m - first_m);       // the last group may be shorter
     const int rin = r - g * group_sz;
-    t.tn = rin / gm;
+    t.tn = gm == p.group_m ? fd_div(rin, p.fd_group_m) : fd_div(rin, p.fd_last_gm);
     t.tm = first_m + (rin - t.tn * gm);
     const int total = p.fold * p.kiters;
     if (p.splits == 1) {
@@ -378,12 +402,13 @@ __device__ __forceinline__ bool work_next(const KParams &p, WorkIter &wi, TileCo
     return false;
 }
 
-__device__ __forceinline__ void batch_coords(int q, int cnt, int d1, int d2, int &c0, int &c1, int &c2) {
-    q = cnt == 1 ? 0 : q % cnt;
-    c2 = q % d2;
-    const int r = q / d2;
-    c1 = r % d1;
-    c0 = r / d1;
+__device__ __forceinline__ void batch_coords(int q, int cnt, int d1, int d2, const FastDiv &fcnt, const FastDiv &fd1,
+                                             const FastDiv &fd2, int &c0, int &c1, int &c2) {
+    q = cnt == 1 ? 0 : q - fd_div(q, fcnt) * cnt;
+    const int r = fd_div(q, fd2);
+    c2 = q - r * d2;
+    c0 = fd_div(r, fd1);
+    c1 = r - c0 * d1;
 }
 
 // Issues the TMA copies of one operand tile.  row0 = first row of the tile, nchunk = tile rows / 32.
@@ -513,8 +538,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     kk = t.it0 - f * p.kiters;
                 }
                 int a0, a1, a2, b0, b1, b2;
-                batch_coords(t.bt * p.fold + f, p.a_batch, p.a_d1, p.a_d2, a0, a1, a2);
-                batch_coords(t.bt * p.fold + f, p.b_batch, p.b_d1, p.b_d2, b0, b1, b2);
+                batch_coords(t.bt * p.fold + f, p.a_batch, p.a_d1, p.a_d2, p.fd_a_cnt, p.fd_a_d1, p.fd_a_d2, a0, a1, a2);
+                batch_coords(t.bt * p.fold + f, p.b_batch, p.b_d1, p.b_d2, p.fd_b_cnt, p.fd_b_d1, p.fd_b_d2, b0, b1, b2);
                 const int rowA = t.tm * (BM * CG) + static_cast<int>(cta_rank) * BM;
                 const int rowB = t.tn * BN + static_cast<int>(cta_rank) * BNL;
                 for (int it = t.it0; it < t.it1; ++it) {
@@ -533,8 +558,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         kk = 0;
                         ++f;
                         if (p.fold > 1) {
-                            batch_coords(t.bt * p.fold + f, p.a_batch, p.a_d1, p.a_d2, a0, a1, a2);
-                            batch_coords(t.bt * p.fold + f, p.b_batch, p.b_d1, p.b_d2, b0, b1, b2);
+                            batch_coords(t.bt * p.fold + f, p.a_batch, p.a_d1, p.a_d2, p.fd_a_cnt, p.fd_a_d1, p.fd_a_d2, a0, a1, a2);
+                            batch_coords(t.bt * p.fold + f, p.b_batch, p.b_d1, p.b_d2, p.fd_b_cnt, p.fd_b_d1, p.fd_b_d2, b0, b1, b2);
                         }
                     }
                 }
@@ -1518,6 +1543,16 @@ int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, in
     k.b_batch = static_cast<int>(p.B.batch);
     k.b_d1 = static_cast<int>(p.B.bshape[1]);
     k.b_d2 = static_cast<int>(p.B.bshape[2]);
+    {
+        const int last_gm = k.tiles_m % k.group_m == 0 ? k.group_m : k.tiles_m % k.group_m;
+        k.fd_splits = make_fastdiv(k.splits);
+        k.fd_per_batch = make_fastdiv(static_cast<long long>(k.tiles_m) * k.tiles_n);
+        k.fd_group_sz = make_fastdiv(static_cast<long long>(k.group_m) * k.tiles_n);
+        k.fd_group_m = make_fastdiv(k.group_m);
+        k.fd_last_gm = make_fastdiv(last_gm);
+        k.fd_a_cnt = make_fastdiv(k.a_batch); k.fd_a_d1 = make_fastdiv(k.a_d1); k.fd_a_d2 = make_fastdiv(k.a_d2);
+        k.fd_b_cnt = make_fastdiv(k.b_batch); k.fd_b_d1 = make_fastdiv(k.b_d1); k.fd_b_d2 = make_fastdiv(k.b_d2);
+    }
     k.stages = pl.stages;
     k.epi_patches = pl.patches;
     k.idesc = (1u << 4) | (2u << 7) | (2u << 10) | (((p.A.k_major || pl.ta) ? 0u : 1u) << 15) |
