@@ -50,9 +50,9 @@ double overlap_work_limit() {
 }
 
 // Row counts up to which the streaming kernels beat the tensor path (measured at K = N = 4096 with a weight
-// that is not in L2: forward 16.5-19.2 vs 23.7 us up to 4 rows and 26.7 vs 23.7 from 5; dx 19.4 vs 23.6 at 5
-// rows and 31.0 vs 23.7 at 8; dW 13.5 vs 16.9 at 8 rows and 21.8 vs 17.0 at 12).
-constexpr int64_t kSkinnyFwdRows = 4, kSkinnyDxRows = 5, kSkinnyDwRows = 8;
+// that is not in L2: dx 19.4 vs 23.6 us at 5 rows and 31.0 vs 23.7 at 8; dW 13.5 vs 16.9 at 8 rows and 21.8 vs
+// 17.0 at 12).  The forward's limit depends on which of its two kernels can run: skinny_fwd_row_limit.
+constexpr int64_t kSkinnyDxRows = 5, kSkinnyDwRows = 8;
 
 bool env_flag(const char *name, int dflt) {
     const char *v = getenv(name);
@@ -316,7 +316,7 @@ int fwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, float *out
     if (s.K == 0) return zero_or_bias_fill(c, out, s.batch * s.M, s.N, bias, accumulate);
 
     const bool want_skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
-                             ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= kSkinnyFwdRows);
+                             ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= skinny_fwd_row_limit(s.N));
     if (want_skinny && s.batch == 1 && skinny_fwd_supported(s.M, s.N, s.K)) {
         const int an = a->ndim, bn = b->ndim;
         const bool a_ok = a->stride[an - 1] == 1 || s.K == 1;
@@ -362,7 +362,7 @@ int fwd_gelu_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const
     const uint32_t saved_flags = c.flags;
     c.flags &= ~static_cast<uint32_t>(MNI_B200_ACCUMULATE_C);
     const bool skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
-                        ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= kSkinnyFwdRows);
+                        ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= skinny_fwd_row_limit(s.N));
     if (s.K > 0 && !skinny) {
         GemmProblem p;
         rc = make_operand(c, *a, false, p.A);

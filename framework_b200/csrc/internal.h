@@ -122,6 +122,7 @@ int read_role_waits(uint64_t out[8], int reset);
 
 // Skinny path (few output rows, HBM-bound): CUDA-core fp32 FMA kernels.
 //   y[M,N] = x[M,K] . W[K,N]          (W row-major, ldw)           M <= 16
+int64_t skinny_fwd_row_limit(int64_t N);
 bool skinny_fwd_supported(int64_t M, int64_t N, int64_t K);
 size_t skinny_fwd_partial_bytes(int64_t M, int64_t N, int64_t K, int sm_count);
 int launch_skinny_fwd(const float *x, int64_t ldx, const float *W, int64_t ldw, float *y, int64_t ldy,

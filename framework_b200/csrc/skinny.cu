@@ -9,6 +9,7 @@
 #include "internal.h"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace mni {
 
@@ -184,6 +185,172 @@ skinny_fwd_kernel(const float *__restrict__ x, long long ldx, const float *__res
     if (threadIdx.x == 0) g_skinny_tickets[blockIdx.x] = 0u;
 }
 
+// ---- forward through a per-thread cp.async ring ----------------------------------------------------
+// Same decomposition as skinny_fwd_kernel (128-column strips x K splits, k-groups inside a block, fused
+// ticket finish), but the weight no longer travels through registers: every thread copies its own
+// 16-byte pieces of W into a private ring in shared memory with cp.async, kRingAhead batches of four
+// rows ahead of the batch it multiplies.  The bytes in flight are then set by the ring, not by the
+// register file, so a thread can keep 16 accumulator vectors (16 rows of x) and still have 192 bytes
+// on their way; and a k-group's chain of dependent DRAM round trips shrinks from one per batch to the
+// ring's fill.  No thread reads another thread's ring slots, so the loop needs no block barrier.
+constexpr int kRingThreads = 256;                           // COLS column-threads x GROUPS k-groups
+constexpr int kRingBatch = 4;                               // rows of W per cp.async group
+// Measured at K = N = 4096 (1 / 8 rows): 8 groups x 4 batches 15.4 / 18.7 us; 4 groups 17.0 / 20.1; 2 groups
+// 17.3 / 25.4; a ring of 6 batches 15.5 / 19.8 (and one block per SM from 8 rows on).
+constexpr int kRingGroups = 8;                              // k-groups per block: 32 column-threads, a 128-column strip
+constexpr int kRingDepth = 4;                               // batches held by the ring, all but one in flight
+constexpr size_t kRingXBytes = 40 * 1024;                   // cap on the staged x slice: two blocks per SM
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem, bool valid) {
+    const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    const int bytes = valid ? 16 : 0;                       // 0: nothing is read, the slot is zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Requires N % 4 == 0, W 16-byte aligned with ldw % 4 == 0, k_per a multiple of kRingUnit.
+template <int MT, int GROUPS, int DEPTH>
+__global__ void __launch_bounds__(kRingThreads, 2)
+skinny_fwd_ring_kernel(const float *__restrict__ x, long long ldx, const float *__restrict__ W, long long ldw,
+                       float *__restrict__ partial, float *__restrict__ y, long long ldy,
+                       const float *__restrict__ bias, int accumulate, int M, long long N, long long K, int k_per,
+                       int x_vec) {
+    extern __shared__ __align__(16) float smem_f[];
+    float *xs = smem_f;                                                  // [MT][k_per], zero beyond M / K
+    float4 *ring = reinterpret_cast<float4 *>(smem_f + MT * k_per);      // [depth * batch][threads]; later the group sums
+    __shared__ unsigned int s_ticket;
+    constexpr int COLS = kRingThreads / GROUPS, AHEAD = DEPTH - 1;
+    const int kg = threadIdx.x / COLS, ct = threadIdx.x % COLS;
+    const long long k0 = static_cast<long long>(blockIdx.y) * k_per;
+    const int kc = static_cast<int>(min(K, k0 + k_per) - k0);
+    const int rpg = k_per / GROUPS;                                 // rows per k-group, a multiple of 4
+    const int g0 = kg * rpg;
+    const int nb = rpg / kRingBatch;
+    const long long col = (static_cast<long long>(blockIdx.x) * COLS + ct) * 4;
+    const bool live = col < N;
+    const float *wp = W + k0 * ldw + (live ? col : 0);
+    float4 *mine = ring + threadIdx.x;
+    auto issue = [&](int b) {
+        if (b < nb) {
+#pragma unroll
+            for (int u = 0; u < kRingBatch; ++u) {
+                const int r = g0 + b * kRingBatch + u;
+                const bool ok = live && r < kc;
+                cp_async16(mine + ((b % DEPTH) * kRingBatch + u) * kRingThreads,
+                           wp + static_cast<long long>(ok ? r : 0) * ldw, ok);
+            }
+        }
+        cp_async_commit();                                               // empty groups keep the count uniform
+    };
+    // The x slice goes first and asynchronously as well (16-byte pieces, zero-filled beyond M rows / kc
+    // columns): staged with ordinary loads its 4 * MT * k_per bytes cost one L2 round trip per few elements
+    // of every thread, which at 16 rows was a third of the kernel's time.
+    if (x_vec) {
+        const int quads = k_per / 4;
+        for (int i = threadIdx.x; i < MT * quads; i += kRingThreads) {
+            const int m = i / quads, kk = (i - m * quads) * 4;
+            const int valid = m < M ? max(0, min(4, kc - kk)) : 0;
+            const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(xs + m * k_per + kk));
+            const float *src = valid > 0 ? x + m * ldx + k0 + kk : x;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid * 4) : "memory");
+        }
+    } else {
+        for (int i = threadIdx.x; i < MT * k_per; i += kRingThreads) {
+            const int m = i / k_per, kk = i - m * k_per;
+            xs[i] = (m < M && kk < kc) ? __ldg(x + m * ldx + k0 + kk) : 0.f;
+        }
+    }
+    cp_async_commit();
+#pragma unroll
+    for (int b = 0; b < AHEAD; ++b) issue(b);
+    cp_async_wait<AHEAD>();                                         // the x slice (oldest group) has landed
+    __syncthreads();
+    float4 acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int b = 0; b < nb; ++b) {
+        issue(b + AHEAD);
+        cp_async_wait<AHEAD>();                                     // batch b has landed
+        float4 w[kRingBatch];
+#pragma unroll
+        for (int u = 0; u < kRingBatch; ++u) w[u] = mine[((b % DEPTH) * kRingBatch + u) * kRingThreads];
+        const float *xr = xs + g0 + b * kRingBatch;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const float4 xv = *reinterpret_cast<const float4 *>(xr + m * k_per);
+            const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int u = 0; u < kRingBatch; ++u) {
+                acc[m].x = fmaf(xa[u], w[u].x, acc[m].x);
+                acc[m].y = fmaf(xa[u], w[u].y, acc[m].y);
+                acc[m].z = fmaf(xa[u], w[u].z, acc[m].z);
+                acc[m].w = fmaf(xa[u], w[u].w, acc[m].w);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                                     // every thread is done with its ring slots
+    float4 *red = ring;                                                  // [groups - 1][MT][cols]
+    if (kg > 0) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) red[((kg - 1) * MT + m) * COLS + ct] = acc[m];
+    }
+    __syncthreads();
+    if (kg == 0 && live) {
+        float *out = partial + static_cast<long long>(blockIdx.y) * M * N;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m >= M) break;
+            float4 a = acc[m];
+#pragma unroll
+            for (int g = 0; g < GROUPS - 1; ++g) {
+                const float4 t = red[(g * MT + m) * COLS + ct];
+                a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+            }
+            __stcg(reinterpret_cast<float4 *>(out + m * N + col), a);
+        }
+    }
+    // Fused finish, as in skinny_fwd_kernel: the block that takes a strip's last ticket adds the strip's
+    // partials in ascending split order; k-group g takes rows g, g + 8, ...
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_ticket = atomicAdd(&g_skinny_tickets[blockIdx.x], 1u);
+    __syncthreads();
+    if (s_ticket != gridDim.y - 1) return;
+    __threadfence();
+    if (live) {
+        const int splits = static_cast<int>(gridDim.y);
+        const long long slab = static_cast<long long>(M) * N;
+        for (int m = kg; m < M; m += GROUPS) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float *src = partial + m * N + col;
+            int sp = 0;
+            for (; sp + 4 <= splits; sp += 4) {                          // 4 independent loads in flight, added in order
+                float4 t[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) t[u] = __ldcg(reinterpret_cast<const float4 *>(src + (sp + u) * slab));
+#pragma unroll
+                for (int u = 0; u < 4; ++u) { sum.x += t[u].x; sum.y += t[u].y; sum.z += t[u].z; sum.w += t[u].w; }
+            }
+            for (; sp < splits; ++sp) {
+                const float4 t = __ldcg(reinterpret_cast<const float4 *>(src + sp * slab));
+                sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+            }
+            const float sv[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = sv[e];
+                if (bias) v += __ldg(bias + col + e);
+                float *dst = y + m * ldy + col + e;
+                *dst = accumulate ? *dst + v : v;
+            }
+        }
+    }
+    if (threadIdx.x == 0) g_skinny_tickets[blockIdx.x] = 0u;
+}
+
 // grid = (n strips of 512 columns, k slabs).  dy[M, 4 cols] lives in registers; each
 // k row of dW is one float4 store per thread.
 template <int MT>
@@ -301,10 +468,48 @@ skinny_dx_kernel(const float *__restrict__ dy, long long lddy, const float *__re
 
 int pick_mt(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16; }
 
-struct FwdPlan { int splits; long long k_per; int strips; };
+struct FwdPlan { int splits; long long k_per; int strips; bool ring; };
+
+// The cp.async-ring kernel takes the aligned problems it was measured faster on (K = N = 4096, weight not in L2:
+// 15.4 vs 17.4 us at 1 row, 16.6 vs 19.0 at 2, 18.7 vs 27.3 at 8; at 3-4 rows the register-staged kernel keeps
+// its 16.4 against 17.1 us).  MNI_B200_SKINNY_RING=0 keeps the register-staged kernel everywhere, =2 takes the
+// ring for every row count.
+int ring_mode() {
+    static const int mode = [] {
+        const char *v = getenv("MNI_B200_SKINNY_RING");
+        return v && *v ? atoi(v) : 1;
+    }();
+    return mode;
+}
+
+bool ring_wanted(int64_t M, int64_t N) {
+    if (ring_mode() == 0 || N % 4 != 0) return false;
+    return ring_mode() == 2 || pick_mt(M) != 4;
+}
+
+FwdPlan ring_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
+    FwdPlan pl;
+    pl.ring = true;
+    const int cols = kRingThreads / kRingGroups, unit = kRingGroups * kRingBatch;
+    pl.strips = static_cast<int>((N + 4 * cols - 1) / (4 * cols));
+    // Two 256-thread blocks per SM in one wave; partial traffic (splits * M * N * 8 bytes) at most a quarter
+    // of the weight traffic (K * N * 4 bytes); every k-group at least one batch deep.
+    const long long want = std::max<long long>(1, (sm_count * 2LL) / pl.strips);
+    const long long cap = std::max<long long>(1, K / (8 * std::max<int64_t>(M, 1)));
+    long long splits = std::min(want, cap);
+    splits = std::min<long long>(splits, std::max<long long>(1, K / unit));
+    long long k_per = ((K + splits - 1) / splits + unit - 1) / unit * unit;
+    const long long k_max = static_cast<long long>(kRingXBytes / sizeof(float) / pick_mt(M)) / unit * unit;
+    k_per = std::min(k_per, std::min<long long>(k_max, 2048));
+    pl.k_per = k_per;
+    pl.splits = static_cast<int>((K + k_per - 1) / k_per);
+    return pl;
+}
 
 FwdPlan fwd_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
+    if (ring_wanted(M, N)) return ring_plan(M, N, K, sm_count);
     FwdPlan pl;
+    pl.ring = false;
     pl.strips = static_cast<int>((N + 4 * kFwdCols - 1) / (4 * kFwdCols));
     // Two 512-thread blocks per SM in total, but keep the partial traffic (splits * M * N * 8 bytes)
     // well under the weight traffic (K * N * 4 bytes) and every k-group at least 8 rows deep.
@@ -322,6 +527,10 @@ FwdPlan fwd_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
 }
 
 }  // namespace
+
+// Rows up to which the streaming forward beats the tensor path (measured at K = N = 4096, weight not in L2:
+// ring kernel 18.7 us at 8 rows, register-staged kernel 26.7 us at 5, tensor path 23.5 us at either).
+int64_t skinny_fwd_row_limit(int64_t N) { return ring_mode() != 0 && N % 4 == 0 ? 8 : 4; }
 
 bool skinny_fwd_supported(int64_t M, int64_t N, int64_t K) {
     return M >= 1 && M <= 16 && N >= 1 && K >= 1;
@@ -343,6 +552,25 @@ int launch_skinny_fwd(const float *x, int64_t ldx, const float *W, int64_t ldw, 
     const bool vec_w = (ldw % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
     if (!vec_w) return fail(MNI_B200_ERR_ARG, "skinny path needs a 16-byte aligned weight with ld %% 4 == 0");
     if (pl.strips > kMaxStrips) return fail(MNI_B200_ERR_ARG, "skinny path: N too large");
+    if (pl.ring) {
+        const size_t ring_smem = static_cast<size_t>(mt) * pl.k_per * sizeof(float) +
+                                 static_cast<size_t>(kRingDepth) * kRingBatch * kRingThreads * sizeof(float4);
+        const bool x_vec = (ldx % 4 == 0 || M == 1) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+#define MNI_SKINNY_RING(MT)                                                                            \
+    case MT:                                                                                           \
+        cudaFuncSetAttribute(skinny_fwd_ring_kernel<MT, kRingGroups, kRingDepth>,                      \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);                 \
+        skinny_fwd_ring_kernel<MT, kRingGroups, kRingDepth><<<grid, kRingThreads, ring_smem, stream>>>( \
+            x, ldx, W, ldw, partial, y, ldy, bias, accumulate ? 1 : 0, (int)M, N, K, (int)pl.k_per,    \
+            x_vec ? 1 : 0);                                                                            \
+        break;
+        switch (mt) {
+            MNI_SKINNY_RING(1) MNI_SKINNY_RING(2) MNI_SKINNY_RING(4) MNI_SKINNY_RING(8) MNI_SKINNY_RING(16)
+        }
+#undef MNI_SKINNY_RING
+        MNI_LAUNCH_CHECK("skinny_fwd_ring_kernel");
+        return MNI_B200_OK;
+    }
 #define MNI_SKINNY_FWD(MT)                                                                             \
     case MT:                                                                                           \
         cudaFuncSetAttribute(skinny_fwd_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \

@@ -247,6 +247,30 @@ def test_skinny_rows(F, oracle, m):
     _check_fwd(F, oracle, x, w, bias=bias)
 
 
+@pytest.mark.parametrize("m,k,n", [(1, 1024, 1024), (2, 333, 260), (3, 64, 128), (5, 1000, 516), (8, 2048, 512),
+                                   (13, 777, 1284), (16, 1, 4), (16, 640, 256), (7, 37, 8), (6, 515, 514),
+                                   (8, 90, 1023), (2, 4100, 36)])
+def test_streaming_forward_kernels_for_every_row_count(F, oracle, m, k, n):
+    """The forced streaming forward (both of its kernels: the cp.async-ring one needs N % 4 == 0) against the
+    oracle: contraction lengths that leave ragged k slices, strips narrower than a block, bias, accumulation,
+    and a second call that must find the finish tickets clean."""
+    rng = np.random.default_rng(300 + m + k + n)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((k, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    skinny = F._lib.FORCE_SKINNY_PATH
+    first = _check_fwd(F, oracle, x, w, flags=skinny)
+    again = _check_fwd(F, oracle, x, w, flags=skinny)
+    assert np.array_equal(first, again)            # fixed summation order
+    with_bias = _check_fwd(F, oracle, x, w, bias=bias, flags=skinny)
+    # c += a.b + bias on top of a known c
+    c0 = rng.standard_normal((m, n), dtype=np.float32)
+    out = _dev(F, c0)
+    F.matmul(_dev(F, x), _dev(F, w), _dev(F, bias), flags=skinny | F._lib.ACCUMULATE_C, out=out)
+    F.device_status()
+    assert np.max(np.abs(out.numpy() - (c0 + with_bias))) <= 1e-5 * max(1.0, float(np.max(np.abs(with_bias))))
+
+
 def test_forced_split_k_and_pack_paths(F, oracle):
     rng = np.random.default_rng(19)
     a = rng.standard_normal((150, 700), dtype=np.float32)
