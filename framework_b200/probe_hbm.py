@@ -88,6 +88,8 @@ def probe_skinny(iters: int) -> None:
                 _time(lambda: F.matmul_backward(dy, x, ws[nxt()], da=dx, need_db=False), iters))
         _report(f"skinny dW  M={m}", 4.0 * k * n,
                 _time(lambda: F.matmul_backward(dy, x, ws[0], db=dws[nxt()], need_da=False), iters))
+    x, y = _tensor(8, k), F.DeviceTensor.empty((8, n))
+    _report("skinny fwd M=8 K=N=4096", 4.0 * k * n, _time(lambda: F.matmul(x, ws[nxt()], out=y), iters))
 
 
 def main() -> None:
