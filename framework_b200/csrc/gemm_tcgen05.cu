@@ -618,45 +618,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     // cycles and would otherwise drain the queue during the wait).
                     const int nstage = stage + 1 == p.stages ? 0 : stage + 1;
                     const uint32_t peek = mbar_test_wait(ready0 + 8u * nstage, stage + 1 == p.stages ? phase ^ 1u : phase);
-                    if constexpr (TA) {
-                        // Narrow tiles retire an MMA every 32 cycles, so this warp's own instruction count
-                        // sets the pace: one election guards the whole k-block's MMAs (one election per
-                        // MMA measured 4 % slower on the attention-shaped products, and a single extra
-                        // uniform branch per k-step 10 %).
-                        const uint32_t at0 = tmem_base + TA_COL0 + static_cast<uint32_t>(stage) * TA_SLOT;
-                        if (elect_one()) {
+                    // This warp's own instruction count sets the pace of narrow tiles (an MMA retires every
+                    // 32 cycles there): one election guards the whole k-block's MMAs and its stage commit
+                    // (one election per MMA measured 12 % slower on the attention-shaped products; wide
+                    // tiles measured the same either way).
+                    if (elect_one()) {
 #pragma unroll
-                            for (int ks = 0; ks < KSTEPS; ++ks) {
-                                const uint32_t at = at0 + ks * 8, bk = b_lo + ks * b_ks;
-                                umma_tf32_ts(d_tmem, at + BK, bk, b_hi, idesc, ks == 0 ? accumulate : 1u);
+                        for (int ks = 0; ks < KSTEPS; ++ks) {
+                            const uint32_t ak = a_lo + ks * a_ks, bk = b_lo + ks * b_ks;
+                            const uint32_t acc_first = ks == 0 ? accumulate : 1u;
+                            if constexpr (TA) {
+                                const uint32_t at = tmem_base + TA_COL0 + static_cast<uint32_t>(stage) * TA_SLOT + ks * 8;
+                                umma_tf32_ts(d_tmem, at + BK, bk, b_hi, idesc, acc_first);
                                 umma_tf32_ts(d_tmem, at, bk + LO16, b_hi, idesc, 1u);
                                 umma_tf32_ts(d_tmem, at, bk, b_hi, idesc, 1u);
+                            } else if constexpr (CG == 2 && FAST) {
+                                umma_tf32_pair(d_tmem, ak, a_hi, bk, b_hi, idesc, acc_first);
+                            } else if constexpr (CG == 2) {
+                                umma_tf32_pair(d_tmem, ak + LO16, a_hi, bk, b_hi, idesc, acc_first);
+                                umma_tf32_pair(d_tmem, ak, a_hi, bk + LO16, b_hi, idesc, 1u);
+                                umma_tf32_pair(d_tmem, ak, a_hi, bk, b_hi, idesc, 1u);
+                            } else if constexpr (FAST) {
+                                umma_tf32(d_tmem, ak, a_hi, bk, b_hi, idesc, acc_first);
+                            } else {
+                                umma_tf32(d_tmem, ak + LO16, a_hi, bk, b_hi, idesc, acc_first);
+                                umma_tf32(d_tmem, ak, a_hi, bk + LO16, b_hi, idesc, 1u);
+                                umma_tf32(d_tmem, ak, a_hi, bk, b_hi, idesc, 1u);
                             }
-                            umma_commit(bar_empty + 8u * stage);
                         }
-                        accumulate = 1u;
-                    } else {
-#pragma unroll
-                    for (int ks = 0; ks < KSTEPS; ++ks) {
-                        const uint32_t ak = a_lo + ks * a_ks, bk = b_lo + ks * b_ks;
-                        if constexpr (CG == 2 && FAST) {
-                            if (elect_one()) umma_tf32_pair(d_tmem, ak, a_hi, bk, b_hi, idesc, accumulate);
-                        } else if constexpr (CG == 2) {
-                            if (elect_one()) umma_tf32_pair(d_tmem, ak + LO16, a_hi, bk, b_hi, idesc, accumulate);
-                            if (elect_one()) umma_tf32_pair(d_tmem, ak, a_hi, bk + LO16, b_hi, idesc, 1u);
-                            if (elect_one()) umma_tf32_pair(d_tmem, ak, a_hi, bk, b_hi, idesc, 1u);
-                        } else if (FAST) {
-                            if (elect_one()) umma_tf32(d_tmem, ak, a_hi, bk, b_hi, idesc, accumulate);
-                        } else {
-                            if (elect_one()) umma_tf32(d_tmem, ak + LO16, a_hi, bk, b_hi, idesc, accumulate);
-                            if (elect_one()) umma_tf32(d_tmem, ak, a_hi, bk + LO16, b_hi, idesc, 1u);
-                            if (elect_one()) umma_tf32(d_tmem, ak, a_hi, bk, b_hi, idesc, 1u);
-                        }
-                        accumulate = 1u;
+                        if constexpr (CG == 2) umma_commit_pair(bar_empty + 8u * stage);
+                        else umma_commit(bar_empty + 8u * stage);
                     }
-                    }
-                    if constexpr (CG == 2) { if (elect_one()) umma_commit_pair(bar_empty + 8u * stage); }
-                    else if constexpr (!TA) { if (elect_one()) umma_commit(bar_empty + 8u * stage); }
+                    accumulate = 1u;
                     next_ready = __all_sync(0xffffffffu, peek != 0u);
                     if (++stage == p.stages) {
                         stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0;
