@@ -271,6 +271,28 @@ def test_streaming_forward_kernels_for_every_row_count(F, oracle, m, k, n):
     assert np.max(np.abs(out.numpy() - (c0 + with_bias))) <= 1e-5 * max(1.0, float(np.max(np.abs(with_bias))))
 
 
+@pytest.mark.parametrize("m,k,n", [(1, 1000, 1024), (2, 333, 260), (3, 67, 128), (4, 1030, 516), (5, 18, 1284),
+                                   (7, 515, 512), (8, 2048, 644), (8, 3, 4), (6, 129, 4100)])
+def test_streaming_backward_kernels_for_every_row_count(F, oracle, m, k, n):
+    """The forced streaming dx and dW kernels against the oracle: row counts on both sides of the switch between
+    the two dx kernels, K that is not a multiple of a block's rows, N that is not a multiple of a warp's 128-column
+    step; then the same call accumulating onto known gradients."""
+    rng = np.random.default_rng(500 + m + k + n)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((k, n), dtype=np.float32)
+    dy = rng.standard_normal((m, n), dtype=np.float32)
+    skinny = F._lib.FORCE_SKINNY_PATH
+    ga, gb = _check_bwd(F, oracle, x, w, dy, flags=skinny)
+    a0 = rng.standard_normal((m, k), dtype=np.float32)
+    b0 = rng.standard_normal((k, n), dtype=np.float32)
+    da, db = _dev(F, a0), _dev(F, b0)
+    F.matmul_backward(_dev(F, dy), _dev(F, x), _dev(F, w), da=da, db=db,
+                      flags=skinny | F._lib.ACCUMULATE_DA | F._lib.ACCUMULATE_DB)
+    F.device_status()
+    assert np.max(np.abs(da.numpy() - (a0 + ga))) <= 1e-5 * max(1.0, float(np.max(np.abs(ga))))
+    assert np.max(np.abs(db.numpy() - (b0 + gb))) <= 1e-5 * max(1.0, float(np.max(np.abs(gb))))
+
+
 def test_forced_split_k_and_pack_paths(F, oracle):
     rng = np.random.default_rng(19)
     a = rng.standard_normal((150, 700), dtype=np.float32)
