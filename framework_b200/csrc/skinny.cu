@@ -210,13 +210,30 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Thread-block-cluster helpers for the ring kernel's finish: the K splits of a strip form one cluster, every
+// CTA leaves its block sums in its own shared memory and the sums are added straight from there.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_cluster_f4(const void *own_smem, unsigned rank) {
+    const unsigned local = static_cast<unsigned>(__cvta_generic_to_shared(own_smem));
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
 // Requires N % 4 == 0, W 16-byte aligned with ldw % 4 == 0, k_per a multiple of kRingUnit.
+// cluster != 0: launched as clusters of gridDim.y CTAs along y (at most 8); the finish then goes through
+// distributed shared memory instead of scratch, fence and ticket, in the same ascending split order.
 template <int MT, int GROUPS, int DEPTH>
 __global__ void __launch_bounds__(kRingThreads, 2)
 skinny_fwd_ring_kernel(const float *__restrict__ x, long long ldx, const float *__restrict__ W, long long ldw,
                        float *__restrict__ partial, float *__restrict__ y, long long ldy,
                        const float *__restrict__ bias, int accumulate, int M, long long N, long long K, int k_per,
-                       int x_vec) {
+                       int x_vec, int cluster) {
     extern __shared__ __align__(16) float smem_f[];
     float *xs = smem_f;                                                  // [MT][k_per], zero beyond M / K
     float4 *ring = reinterpret_cast<float4 *>(smem_f + MT * k_per);      // [depth * batch][threads]; later the group sums
@@ -293,12 +310,13 @@ skinny_fwd_ring_kernel(const float *__restrict__ x, long long ldx, const float *
     cp_async_wait<0>();
     __syncthreads();                                                     // every thread is done with its ring slots
     float4 *red = ring;                                                  // [groups - 1][MT][cols]
+    float4 *mine_sums = ring + (GROUPS - 1) * MT * COLS;                 // [MT][cols]: this block's sums (cluster finish)
     if (kg > 0) {
 #pragma unroll
         for (int m = 0; m < MT; ++m) red[((kg - 1) * MT + m) * COLS + ct] = acc[m];
     }
     __syncthreads();
-    if (kg == 0 && live) {
+    if (kg == 0) {
         float *out = partial + static_cast<long long>(blockIdx.y) * M * N;
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
@@ -309,8 +327,33 @@ skinny_fwd_ring_kernel(const float *__restrict__ x, long long ldx, const float *
                 const float4 t = red[(g * MT + m) * COLS + ct];
                 a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
             }
-            __stcg(reinterpret_cast<float4 *>(out + m * N + col), a);
+            if (cluster) mine_sums[m * COLS + ct] = a;
+            else if (live) __stcg(reinterpret_cast<float4 *>(out + m * N + col), a);
         }
+    }
+    if (cluster) {
+        // Rows are dealt out over (CTA rank, k-group); a row's splits are added in ascending rank = split order.
+        cluster_sync_all();
+        const int ranks = static_cast<int>(gridDim.y);
+        if (live) {
+            for (int m = static_cast<int>(blockIdx.y) * GROUPS + kg; m < M; m += ranks * GROUPS) {
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int r = 0; r < ranks; ++r) {
+                    const float4 t = ld_cluster_f4(mine_sums + m * COLS + ct, static_cast<unsigned>(r));
+                    sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+                }
+                const float sv[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float v = sv[e];
+                    if (bias) v += __ldg(bias + col + e);
+                    float *dst = y + m * ldy + col + e;
+                    *dst = accumulate ? *dst + v : v;
+                }
+            }
+        }
+        cluster_sync_all();                                              // no CTA leaves while its sums may still be read
+        return;
     }
     // Fused finish, as in skinny_fwd_kernel: the block that takes a strip's last ticket adds the strip's
     // partials in ascending split order; k-group g takes rows g, g + 8, ...
@@ -468,12 +511,11 @@ skinny_dx_kernel(const float *__restrict__ dy, long long lddy, const float *__re
 
 int pick_mt(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16; }
 
-struct FwdPlan { int splits; long long k_per; int strips; bool ring; };
+struct FwdPlan { int splits; long long k_per; int strips; bool ring; bool cluster = false; };
 
-// The cp.async-ring kernel takes the aligned problems it was measured faster on (K = N = 4096, weight not in L2:
-// 15.4 vs 17.4 us at 1 row, 16.6 vs 19.0 at 2, 18.7 vs 27.3 at 8; at 3-4 rows the register-staged kernel keeps
-// its 16.4 against 17.1 us).  MNI_B200_SKINNY_RING=0 keeps the register-staged kernel everywhere, =2 takes the
-// ring for every row count.
+// The cp.async-ring kernel takes every aligned problem (K = N = 4096, weight not in L2, cluster finish:
+// 14.2 / 14.6 / 15.8 / 17.7 us at 1 / 2 / 4 / 8 rows against 17.4 / 19.0 / 16.4 / 27.3 us for the
+// register-staged kernel).  MNI_B200_SKINNY_RING=0 keeps the register-staged kernel everywhere.
 int ring_mode() {
     static const int mode = [] {
         const char *v = getenv("MNI_B200_SKINNY_RING");
@@ -483,8 +525,8 @@ int ring_mode() {
 }
 
 bool ring_wanted(int64_t M, int64_t N) {
-    if (ring_mode() == 0 || N % 4 != 0) return false;
-    return ring_mode() == 2 || pick_mt(M) != 4;
+    (void)M;
+    return ring_mode() != 0 && N % 4 == 0;
 }
 
 FwdPlan ring_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
@@ -501,8 +543,20 @@ FwdPlan ring_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
     long long k_per = ((K + splits - 1) / splits + unit - 1) / unit * unit;
     const long long k_max = static_cast<long long>(kRingXBytes / sizeof(float) / pick_mt(M)) / unit * unit;
     k_per = std::min(k_per, std::min<long long>(k_max, 2048));
+    // Up to 8 splits can finish as one thread-block cluster through distributed shared memory; a plan of 9-12
+    // splits is rounded down to 8 when the longer k slice still fits (MNI_B200_RING_CLUSTER=0: ticket finish only).
+    static const bool cluster_on = [] {
+        const char *v = getenv("MNI_B200_RING_CLUSTER");
+        return !(v && *v) || atoi(v) != 0;
+    }();
+    if (cluster_on) {
+        const long long k8 = ((K + 7) / 8 + unit - 1) / unit * unit;
+        const long long n_now = (K + k_per - 1) / k_per;
+        if (n_now > 8 && n_now <= 12 && k8 <= std::min<long long>(k_max, 2048)) k_per = k8;
+    }
     pl.k_per = k_per;
     pl.splits = static_cast<int>((K + k_per - 1) / k_per);
+    pl.cluster = cluster_on && pl.splits >= 2 && pl.splits <= 8;
     return pl;
 }
 
@@ -529,7 +583,7 @@ FwdPlan fwd_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
 }  // namespace
 
 // Rows up to which the streaming forward beats the tensor path (measured at K = N = 4096, weight not in L2:
-// ring kernel 18.7 us at 8 rows, register-staged kernel 26.7 us at 5, tensor path 23.5 us at either).
+// ring kernel 17.7 us at 8 rows, register-staged kernel 26.7 us at 5, tensor path 20-23.5 us at either).
 int64_t skinny_fwd_row_limit(int64_t N) { return ring_mode() != 0 && N % 4 == 0 ? 8 : 4; }
 
 bool skinny_fwd_supported(int64_t M, int64_t N, int64_t K) {
@@ -556,13 +610,27 @@ int launch_skinny_fwd(const float *x, int64_t ldx, const float *W, int64_t ldw, 
         const size_t ring_smem = static_cast<size_t>(mt) * pl.k_per * sizeof(float) +
                                  static_cast<size_t>(kRingDepth) * kRingBatch * kRingThreads * sizeof(float4);
         const bool x_vec = (ldx % 4 == 0 || M == 1) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kRingThreads);
+        cfg.dynamicSmemBytes = ring_smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = static_cast<unsigned>(pl.splits);
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pl.cluster ? 1 : 0;
+        const int acc_i = accumulate ? 1 : 0, m_i = static_cast<int>(M), kper_i = static_cast<int>(pl.k_per);
+        const int xvec_i = x_vec ? 1 : 0, cluster_i = pl.cluster ? 1 : 0;
+        const long long ldx_l = ldx, ldw_l = ldw, ldy_l = ldy, n_l = N, k_l = K;
 #define MNI_SKINNY_RING(MT)                                                                            \
     case MT:                                                                                           \
         cudaFuncSetAttribute(skinny_fwd_ring_kernel<MT, kRingGroups, kRingDepth>,                      \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);                 \
-        skinny_fwd_ring_kernel<MT, kRingGroups, kRingDepth><<<grid, kRingThreads, ring_smem, stream>>>( \
-            x, ldx, W, ldw, partial, y, ldy, bias, accumulate ? 1 : 0, (int)M, N, K, (int)pl.k_per,    \
-            x_vec ? 1 : 0);                                                                            \
+        cudaLaunchKernelEx(&cfg, skinny_fwd_ring_kernel<MT, kRingGroups, kRingDepth>, x, ldx_l, W, ldw_l, partial, \
+                           y, ldy_l, bias, acc_i, m_i, n_l, k_l, kper_i, xvec_i, cluster_i);           \
         break;
         switch (mt) {
             MNI_SKINNY_RING(1) MNI_SKINNY_RING(2) MNI_SKINNY_RING(4) MNI_SKINNY_RING(8) MNI_SKINNY_RING(16)
