@@ -1,18 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the matmul hot path: f32 matmul forward+backward TFLOP/s.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4] [--impl reference]
 
 One "step" is one forward+backward pass of the workload through the C ABI of
-libmni_b200.so.  The default workload is the Linear-layer training step
-(x[4096,1024] . W[1024,4096] + b, backward with dy ~N(0,1) giving dx, dW, db).  With
-N > 1 every rank runs the step on its own batch shard and the weight and bias
-gradients are summed onto rank 0 with an NCCL reduce (data parallel, weak scaling).
+libmni_b200.so.  The default workload is the broadcast-weight GEMM
+(activations [64,1024,768] . weight [768,3072], backward summing dW over the batch), the
+configuration that shards: with N > 1 the 64 batches are split over the ranks (strong
+scaling, one rank per GPU), every rank runs forward, dW and dA on its shard, and dW is
+summed onto rank 0 with one NCCL reduce that overlaps the dA GEMM.  `--workload c5a` shards
+the 8192^3 square by rows of A and reduces dB in row panels as they complete; `--workload c2`
+is the Linear training step, weak-scaled; c1 / c3 / c5b* run as replicas; `softmax` and
+`adamw` time the pointwise neighbours of the path in GB/s.
 
 The JSON line carries: `value` (device-resident inputs, CUDA-event timing, max over
 ranks), `e2e` (pinned host buffers in, host buffers out, copies inside the timed
-region), `roofline` of the dominant kernel, and `cpu_baseline` (the CPU oracle, a
-restatement of the reference's single-threaded CPU backend, timed on this host).
+region), `roofline` of the dominant kernel plus `kernels` (every product of the step timed
+alone against its own roofline), and `cpu_baseline` (the CPU oracle, a restatement of the
+reference's single-threaded CPU backend, timed on this host on a bounded sample).
 `--impl reference` times that CPU implementation alone, on all host cores.
 """
 from __future__ import annotations
@@ -43,6 +48,7 @@ class Workload:
     kind "gemm": y = a . b (+ bias); backward from dy gives da, db (, dbias).
     kind "attention": S = q . k^T (k^T a stride-only permute view), O = S . v; backward from dO
     gives dS, dV, dQ, dK^T -- the six GEMMs of the attention-shaped configuration.
+    kind "softmax" / "adamw": the pointwise neighbours of the path (HBM-bound; reported in GB/s).
     """
 
     def __init__(self, name, desc, a_shape, b_shape, *, bias=False, b_perm=None, dist_a="normal",
@@ -117,26 +123,65 @@ WORKLOADS = {
     "c5b1": Workload("c5b1", "skinny M=1, K=N=4096", (1, 4096), (4096, 4096)),
     "c5b4": Workload("c5b4", "skinny M=4, K=N=4096", (4, 4096), (4096, 4096)),
     "c5b16": Workload("c5b16", "skinny M=16, K=N=4096", (16, 4096), (4096, 4096)),
+    "softmax": Workload("softmax", "row softmax fwd+bwd over the attention scores [8,12,512,512]",
+                        (8, 12, 512, 512), (1, 1), kind="softmax"),
+    "adamw": Workload("adamw", "gradient norm + clipped AdamW step on a [768,3072] weight and 64 M elements",
+                      (64 * 1024 * 1024,), (1, 1), kind="adamw"),
 }
 HBM_BOUND = ("c3", "c5b1", "c5b4", "c5b16")
-# DRAM bytes per forward launch from ncu captures of the same launch
-# (dram__bytes_read.sum + dram__bytes_write.sum; 3xTF32 build with CTA pairs).
-NCU_TRAFFIC_BYTES = {"c2": 34.11e6 + 19.63e6}
+SHARDED = ("c4", "c5a")            # partition across ranks (strong scaling); c2 is weak-scaled; the rest are replicas
+# DRAM bytes of one forward launch, from ncu captures of that launch summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum): a cited capture, not a measurement of this run.
+NCU_TRAFFIC = {
+    "c2": (34.11e6 + 19.63e6, "profiles/gemm_tc_kernel_c2_linear.md"),
+}
+C5A_PANELS = 4                      # row panels of dB, each reduced as soon as it is computed
 
 
 def shard_workload(wl: Workload, rank: int, world: int) -> Workload:
     """Per-rank shard for the configurations that partition: batch shards for c4, row shards for
     c5a.  c2 is weak-scaled (every rank owns a full-size batch shard), the rest run as replicas."""
-    if world == 1 or wl.name not in ("c4", "c5a"):
+    if world == 1 or wl.name not in SHARDED:
         return wl
     from framework_b200.sharding import shard_leading
     return wl.with_a_shape(shard_leading(wl.a_shape, rank, world), f" (1/{world} shard)")
 
 
-class Problem:
-    """Device-side instance of a workload: resident inputs, preallocated outputs, the call sequence."""
+def config_dict(base: Workload, world: int, precision: str) -> dict:
+    """The `config` object: the same for this arm and for the reference arm."""
+    if base.kind in ("softmax", "adamw"):
+        par = "single GPU" if world == 1 else f"{world} replicas"
+    elif world == 1:
+        par = "single GPU"
+    elif base.name == "c4":
+        par = f"dp{world}: 64/{world} batches per rank, one NCCL reduce of dW (flat buffer) overlapped with the dA GEMM"
+    elif base.name == "c5a":
+        par = (f"dp{world}: 8192/{world} rows of A per rank, dB computed in {C5A_PANELS} row panels, each NCCL-reduced "
+               "as it completes, overlapped with the next panel and the dA GEMM")
+    elif base.name == "c2":
+        par = f"dp{world}: one full-size batch shard per rank (weak), one NCCL reduce of dW+db (flat buffer)"
+    else:
+        par = f"{world} replicas (the configuration does not shard)"
+    ws = working_set_mb(base)
+    return {"workload": f"{base.name}: {base.desc}", "shapes": f"{base.a_shape} x {base.b_logical}",
+            "parallelism": par, "precision": precision,
+            "l2": (f"working set {ws:.0f} MB per step vs 126 MB L2, no flush" if ws > 126 else
+                   f"working set {ws:.0f} MB fits the 126 MB L2; not flushed between steps (stated)"),
+            "flops_per_step": base.flops if base.name in SHARDED else base.flops * world}
 
-    def __init__(self, F, wl: Workload, host: dict, dev, flags: int):
+
+def scaling_label(base: Workload) -> str:
+    return "strong" if base.name in SHARDED else "weak"
+
+
+class Problem:
+    """Device-side instance of a workload: resident inputs, preallocated outputs, the call sequence.
+
+    The gradients that are summed over ranks (dW, db) are views of ONE flat buffer, so that a step
+    needs one collective call for them."""
+
+    def __init__(self, F, wl: Workload, host: dict, dev, flags: int, panels: int = 1):
+        import torch
         T = F.DeviceTensor
         self.F, self.wl, self.flags = F, wl, flags
         self.inp = {k: T.from_numpy(v, dev) for k, v in host.items()}
@@ -146,12 +191,25 @@ class Problem:
             self.out = {"s": T.empty(shp, dev), "o": T.empty(wl.a_shape, dev), "ds": T.empty(shp, dev),
                         "dv": T.empty(wl.a_shape, dev), "dq": T.empty(wl.a_shape, dev),
                         "dkt": T.empty(self.kt.shape, dev)}
-        else:
-            self.b = self.inp["b"].permute(wl.b_perm) if wl.b_perm else self.inp["b"]
-            self.out = {"y": T.empty(wl.out_shape, dev), "da": T.empty(wl.a_shape, dev),
-                        "db": T.empty(self.b.shape, dev)}
-            if wl.bias:
-                self.out["dbias"] = T.empty((wl.mkn[2],), dev)
+            return
+        self.b = self.inp["b"].permute(wl.b_perm) if wl.b_perm else self.inp["b"]
+        n_w = int(np.prod(self.b.shape))
+        n_b = wl.mkn[2] if wl.bias else 0
+        off_b = (n_w + 63) // 64 * 64                       # 256-byte aligned start of db inside the flat buffer
+        self.grad_flat = torch.empty(off_b + n_b if n_b else n_w, dtype=torch.float32, device=dev)
+        self.out = {"y": T.empty(wl.out_shape, dev), "da": T.empty(wl.a_shape, dev),
+                    "db": T(self.grad_flat[:n_w], self.b.shape)}
+        if wl.bias:
+            self.out["dbias"] = T(self.grad_flat[off_b:off_b + n_b], (n_b,))
+        # Row panels of the weight gradient (2-D problems): rows [lo, hi) of dB = A[:, lo:hi]^T . dC need the
+        # matching columns of A and land contiguously in the flat buffer.
+        self.panels = []
+        if panels > 1 and len(wl.a_shape) == 2 and not wl.bias:
+            from framework_b200.sharding import panel_bounds
+            k, n = self.b.shape
+            for lo, hi in panel_bounds(k, panels, multiple=128):
+                self.panels.append((self.inp["a"].narrow(1, lo, hi - lo), self.b.narrow(0, lo, hi - lo),
+                                    T(self.grad_flat[lo * n:hi * n], (hi - lo, n)), self.grad_flat[lo * n:hi * n]))
 
     def forward(self):
         F, i, o = self.F, self.inp, self.out
@@ -176,12 +234,43 @@ class Problem:
         self.F.matmul_backward(i["dy"], i["a"], self.b, flags=self.flags, need_da=False, db=o["db"],
                                dbias=o.get("dbias"), want_dbias=self.wl.bias)
 
+    def backward_weight_panel(self, p: int):
+        a_cols, b_rows, db_rows, _ = self.panels[p]
+        self.F.matmul_backward(self.inp["dy"], a_cols, b_rows, flags=self.flags, need_da=False, db=db_rows)
+
     def backward_inputs(self):
         i, o = self.inp, self.out
         self.F.matmul_backward(i["dy"], i["a"], self.b, flags=self.flags, da=o["da"], need_db=False)
 
-    def weight_grads(self):
-        return [self.out[k].storage for k in ("db", "dbias") if k in self.out]
+    def products(self):
+        """Every GEMM of the step as (label, callable, algorithmic bytes, flops): each operand read once, the
+        output written once."""
+        F, i, o, fl = self.F, self.inp, self.out, self.flags
+        wl = self.wl
+        m, k, n = wl.mkn
+        one = 2 * m * n * k * wl.batch
+
+        def nbytes(*ts):
+            return 4.0 * sum(int(np.prod(t.shape)) for t in ts)
+        if wl.kind == "attention":
+            return [
+                ("S = Q.K^T", lambda: F.matmul(i["q"], self.kt, flags=fl, out=o["s"]), nbytes(i["q"], i["k"], o["s"]), one),
+                ("O = S.V", lambda: F.matmul(o["s"], i["v"], flags=fl, out=o["o"]), nbytes(o["s"], i["v"], o["o"]), one),
+                ("dS = dO.V^T", lambda: F.matmul_backward(i["do"], o["s"], i["v"], flags=fl, da=o["ds"], need_db=False),
+                 nbytes(i["do"], i["v"], o["ds"]), one),
+                ("dV = S^T.dO", lambda: F.matmul_backward(i["do"], o["s"], i["v"], flags=fl, need_da=False, db=o["dv"]),
+                 nbytes(o["s"], i["do"], o["dv"]), one),
+                ("dQ = dS.K", lambda: F.matmul_backward(o["ds"], i["q"], self.kt, flags=fl, da=o["dq"], need_db=False),
+                 nbytes(o["ds"], i["k"], o["dq"]), one),
+                ("dK^T = Q^T.dS", lambda: F.matmul_backward(o["ds"], i["q"], self.kt, flags=fl, need_da=False, db=o["dkt"]),
+                 nbytes(i["q"], o["ds"], o["dkt"]), one),
+            ]
+        return [
+            ("forward y = a.b" + (" + bias" if wl.bias else ""), self.forward, nbytes(i["a"], self.b, o["y"]), one),
+            ("grad_a = dy.b^T", self.backward_inputs, nbytes(i["dy"], self.b, o["da"]), one),
+            ("grad_b = a^T.dy" + (" (+ dbias)" if wl.bias else "") + (" (batch folded into K)" if wl.batch > 1 and len(wl.b_shape) == 2 else ""),
+             self.backward_weights, nbytes(i["a"], i["dy"], o["db"]), one),
+        ]
 
 
 # --------------------------------------------------------------------------- clocks
@@ -286,12 +375,20 @@ class ClockSampler:
                 "source": "nvidia-smi -lms 50"}
 
 
+def load_peaks() -> dict:
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f)
+    except OSError:
+        return {}
+
+
 # --------------------------------------------------------------------------- GPU arm
 def run_ours(args):
     import torch
     import torch.distributed as dist
     import framework_b200 as F
-    from framework_b200.sharding import reduce_to_root
+    from framework_b200.sharding import DataParallelStep
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -304,7 +401,15 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     base = WORKLOADS[args.workload]
+    if base.kind in ("softmax", "adamw"):
+        run_pointwise(args, F, base, dev, world, rank)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     wl = shard_workload(base, rank, world)
+    if world == 1 and args.shard_of > 1:     # one rank's shard of an N-rank run, alone on this GPU (no reduce): kernel tuning
+        wl = shard_workload(base, 0, args.shard_of)
     flags = F._lib.PRECISION_TF32 if args.precision == "tf32" else 0
     host = wl.host_inputs(seed=rank)
     if world > 1 and wl.kind == "gemm":      # the weight (and bias) are replicated
@@ -312,33 +417,35 @@ def run_ours(args):
         for key in ("b", "bias"):
             if key in host:
                 host[key] = shared[key]
-    prob = Problem(F, wl, host, dev, flags)
     reduce_grads = world > 1 and wl.name in ("c2", "c4", "c5a")
+    n_panels = C5A_PANELS if (reduce_grads and wl.name == "c5a") else 1
+    prob = Problem(F, wl, host, dev, flags, panels=n_panels)
 
-    # Data parallel: the weight gradient is computed first and summed onto rank 0 on a second stream
-    # while the input-gradient GEMM (and the next step's forward) run.
+    # Data parallel: the weight gradient is computed first (for c5a in row panels) and summed onto rank 0 on a
+    # second stream while the next panel, the input-gradient GEMM and the next step's forward run.
     comm = torch.cuda.Stream() if reduce_grads else None
-    ev_w, ev_red = torch.cuda.Event(), torch.cuda.Event()
 
-    def eager_step(pr=prob):
-        pr.forward()
+    def make_step(pr):
+        if wl.kind == "attention":
+            def plain():
+                pr.forward()
+                pr.backward()
+            plain.join = lambda: None
+            return plain
         if not reduce_grads:
-            pr.backward()
-            return
-        main = torch.cuda.current_stream()
-        main.wait_event(ev_red)              # the previous reduce is done with the gradient buffers
-        pr.backward_weights()
-        ev_w.record(main)
-        with torch.cuda.stream(comm):
-            comm.wait_event(ev_w)
-            for g in pr.weight_grads():
-                reduce_to_root(g, dst=0)
-            ev_red.record(comm)
-        pr.backward_inputs()
+            def plain():
+                pr.forward()
+                pr.backward()
+            plain.join = lambda: None
+            return plain
+        if pr.panels:
+            fns = [(lambda p=p: pr.backward_weight_panel(p)) for p in range(len(pr.panels))]
+            bufs = [p[3] for p in pr.panels]
+        else:
+            fns, bufs = [pr.backward_weights], [pr.grad_flat]
+        return DataParallelStep(pr.forward, fns, bufs, pr.backward_inputs, streams=(torch.cuda.current_stream(), comm))
 
-    def join_comm():
-        if reduce_grads:
-            torch.cuda.current_stream().wait_event(ev_red)
+    eager_step = make_step(prob)
 
     def barrier():
         if world > 1:
@@ -363,11 +470,13 @@ def run_ours(args):
     warmup = max(args.warmup, 3)
     for _ in range(warmup):
         eager_step()
+    eager_step.join()
     F.device_status()
 
     # Launch-bound workloads replay the step from a CUDA graph (same kernels, same order).
     step, graphed = eager_step, False
-    est_ms = timed(eager_step, 5) / 5
+    est_ms = timed(eager_step, 5, after=eager_step.join) / 5
+    eager_ms = est_ms
     if world == 1 and args.graph != "off" and (args.graph == "on" or est_ms < 0.2):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -381,6 +490,7 @@ def run_ours(args):
         for _ in range(3):
             step()
         F.device_status()
+        eager_ms = timed(eager_step, 50) / 50
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -389,52 +499,82 @@ def run_ours(args):
     launches0 = F.launch_count()
     eager_step()
     launches_per_step = F.launch_count() - launches0
+    eager_step.join()
     torch.cuda.synchronize()
     t_wall0 = time.time()
-    total_ms = timed(step, args.steps, after=join_comm)
+    total_ms = timed(step, args.steps, after=eager_step.join)
     t_wall1 = time.time()
     F.device_status()
     ms_per_step = total_ms / args.steps
     value = wl.flops * world / (ms_per_step * 1e-3) / 1e12
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
-    # ---- roofline of the dominant kernel: the forward launch(es) timed alone ----
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except OSError:
-        pass
-    # The forward launch is timed alone, against the burst peak: let the power state of the timed region
-    # above (which ends at the power cap) settle first.
+
+    # ---- phase timeline of one step on rank 0 (multi-GPU only): where the reduce sits beside the GEMMs -----
+    timeline = None
+    if reduce_grads:
+        marks = []
+
+        def mark(label, stream):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(stream)
+            marks.append((label, ev))
+        for _ in range(2):
+            marks.clear()
+            barrier()
+            eager_step(mark)
+            eager_step.join()
+            barrier()
+        if rank == 0:
+            t0 = marks[0][1]
+            timeline = {label: round(t0.elapsed_time(ev) * 1e3, 1) for label, ev in marks}
+            timeline["unit"] = "us after step begin, rank 0, one eager step between barriers"
+
+    # ---- rooflines: every product of the step timed alone (burst clocks: let the power state settle first) ----
+    peaks = load_peaks()
     torch.cuda.synchronize()
     time.sleep(0.5)
-    l0 = F.launch_count()
-    prob.forward()
-    fwd_launches = F.launch_count() - l0
-    fwd_steps = min(args.steps, 50)
-    fwd_ms = timed(prob.forward, fwd_steps) / fwd_steps
-    if wl.name in HBM_BOUND:
-        if wl.kind == "attention":   # S written and read once, Q, K, V read, O written
-            alg_bytes = 4.0 * (2 * np.prod(wl.out_shape) + 4 * np.prod(wl.a_shape))
-        else:                        # each operand read once, the output written once
-            alg_bytes = 4.0 * (np.prod(wl.a_shape) + np.prod(wl.b_shape) + np.prod(wl.out_shape))
-        peak = peaks.get("hbm_gbs", 6650.0)
-        achieved = alg_bytes / (fwd_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": None, "kernel": "forward call(s): " + ("gemm_tc_kernel x2" if wl.kind == "attention"
-                                                                      else "skinny_fwd_kernel + reduce"),
-                    "launches_per_call": fwd_launches, "algorithmic_bytes": alg_bytes,
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    tf32_peak = peaks.get("bf16_tflops", 1590.0) / 2.0
+    hbm_bound = wl.name in HBM_BOUND
+    kernels = []
+    reps = max(5, min(args.steps, 50))
+    for label, fn, alg_bytes, flops in prob.products():
+        l0 = F.launch_count()
+        fn()
+        n_launch = F.launch_count() - l0
+        ms = timed(fn, reps) / reps
+        gbs = alg_bytes / (ms * 1e-3) / 1e9
+        tfs = flops / (ms * 1e-3) / 1e12
+        entry = {"call": label, "us": round(ms * 1e3, 2), "launches": n_launch, "tflops": round(tfs, 2),
+                 "gbs": round(gbs, 1), "algorithmic_bytes": alg_bytes}
+        if hbm_bound:
+            entry.update(bound="hbm", frac=round(gbs / hbm_peak, 4))
+        else:
+            issued = tfs * (1 if args.precision == "tf32" else 3)
+            entry.update(bound="tensor", frac=round(tfs / tf32_peak, 4), issued_frac=round(issued / tf32_peak, 4))
+        kernels.append(entry)
+    first = kernels[0]
+    if hbm_bound:
+        total_bytes = sum(k["algorithmic_bytes"] for k in kernels)
+        total_us = sum(k["us"] for k in kernels)
+        roofline = {"bound": "hbm", "achieved": first["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                    "frac": first["gbs"] / hbm_peak, "traffic": None,
+                    "kernel": f"{first['call']} ({first['launches']} launch(es); the other products are in `kernels`)",
+                    "algorithmic_bytes": first["algorithmic_bytes"],
+                    "all_products": {"gbs": round(total_bytes / (total_us * 1e-6) / 1e9, 1),
+                                     "frac": round(total_bytes / (total_us * 1e-6) / 1e9 / hbm_peak, 4),
+                                     "note": "sum of algorithmic bytes / sum of the products' stand-alone times"},
                     "peak_source": "measured hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650"}
     else:
-        bf16 = peaks.get("bf16_tflops", 1590.0)
-        peak = bf16 / 2.0
-        achieved = wl.fwd_flops / (fwd_ms * 1e-3) / 1e12
-        issued = achieved * (1 if args.precision == "tf32" else 3)
-        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "traffic": NCU_TRAFFIC_BYTES.get(wl.name) if args.precision != "tf32" else None,
-                    "traffic_unit": "bytes per launch (ncu dram read+write)",
-                    "algorithmic_bytes": 4.0 * (np.prod(wl.a_shape) + np.prod(wl.b_shape) + np.prod(wl.out_shape)),
-                    "kernel": "gemm_tc_kernel (forward GEMM launch, bias fused)",
-                    "issued_tflops": issued, "issued_frac": issued / peak,
+        traffic, source = NCU_TRAFFIC.get(wl.name, (None, None)) if (args.precision != "tf32" and world == 1) else (None, None)
+        issued = first["tflops"] * (1 if args.precision == "tf32" else 3)
+        roofline = {"bound": "tensor", "achieved": first["tflops"], "peak": tf32_peak, "unit": "TFLOP/s",
+                    "frac": first["tflops"] / tf32_peak, "traffic": traffic,
+                    "traffic_source": (f"cited from {source} (ncu dram read+write bytes of this launch), not measured by this run"
+                                       if source else None),
+                    "algorithmic_bytes": first["algorithmic_bytes"],
+                    "kernel": f"gemm_tc_kernel ({first['call']}; the other products are in `kernels`)",
+                    "issued_tflops": issued, "issued_frac": issued / tf32_peak,
                     "note": ("3xTF32 issues 3 MMAs per product: algorithmic ceiling = peak/3"
                              if args.precision != "tf32" else "single-pass TF32"),
                     "peak_source": ("measured bf16_tflops/2 (no TF32 figure in MEASURED_PEAKS.json)"
@@ -449,7 +589,8 @@ def run_ours(args):
     h2d = sum(h.numel() * 4 for h in h_in.values())
     d2h = sum(h.numel() * 4 for h in h_out.values())
     s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
-    slots = [prob, Problem(F, wl, host, dev, flags)]
+    slots = [prob, Problem(F, wl, host, dev, flags, panels=n_panels)]
+    slot_steps = [eager_step, make_step(slots[1])]
     ev_in = [torch.cuda.Event() for _ in slots]
     ev_done = [torch.cuda.Event() for _ in slots]
     ev_out = [torch.cuda.Event() for _ in slots]
@@ -466,8 +607,8 @@ def run_ours(args):
             ev_in[i].record(s_in)
         s_main.wait_event(ev_in[i])
         s_main.wait_event(ev_out[i])             # the download that last read this slot's outputs is done
-        eager_step(pr)
-        join_comm()
+        slot_steps[i]()
+        slot_steps[i].join()
         ev_done[i].record(s_main)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_done[i])
@@ -477,7 +618,6 @@ def run_ours(args):
             ev_out[i].record(s_out)
 
     def e2e_join():
-        join_comm()
         s_main.wait_stream(s_in)
         s_main.wait_stream(s_out)
 
@@ -490,20 +630,23 @@ def run_ours(args):
     e2e_value = wl.flops * world / (e2e_ms * 1e-3) / 1e12
     F.device_status()
 
-    # Last measurement of the run (it heats the GPU to its power cap).  NVML refreshes its clock and throttle readings far more slowly than a timed region of ~0.1 s lasts, so
-    # the same steps are repeated, untimed, for about a second with a second sampler: what the clocks settle
-    # at under this workload, reported beside the readings taken during the timed region.
+    # Last measurement of the run (it heats the GPU to its power cap).  NVML refreshes its clock and throttle
+    # readings far more slowly than a timed region of ~0.1 s lasts, so the same steps are repeated, untimed, for
+    # about a second with a second sampler: what the clocks settle at under this workload, reported beside the
+    # readings taken during the timed region.
     sustain_steps = int(min(20000, max(args.steps, 1000.0 / max(ms_per_step, 1e-3))))
     sustain = ClockSampler(local_rank)
     if rank == 0:
         sustain.start()
     t_s0 = time.time()
-    sustain_ms = timed(step, sustain_steps, after=join_comm)
+    sustain_ms = timed(step, sustain_steps, after=eager_step.join)
     t_s1 = time.time()
     if rank == 0:
         settled = sustain.stop(t_s0 + 0.5 * (t_s1 - t_s0), t_s1)       # second half of the window
         clocks["sustained"] = {"seconds": round(t_s1 - t_s0, 2), "steps": sustain_steps,
-                               "ms_per_step": sustain_ms / sustain_steps, "sm_mhz": settled.get("sm_mhz"),
+                               "ms_per_step": sustain_ms / sustain_steps,
+                               "value": wl.flops * world / (sustain_ms / sustain_steps * 1e-3) / 1e12,
+                               "sm_mhz": settled.get("sm_mhz"),
                                "sm_min_mhz": settled.get("sm_min_mhz"), "power_w_max": settled.get("power_w_max"),
                                "reasons": settled.get("reasons"), "samples": settled.get("samples")}
         for r in settled.get("reasons") or []:
@@ -512,29 +655,27 @@ def run_ours(args):
 
     if rank == 0:
         cpu = cpu_baseline_sample(base, threads=1) if (world == 1 and not args.no_cpu) else None
-        ws = working_set_mb(wl)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong" if base.name in ("c4", "c5a") else "weak", "vs_baseline": None,
+            "scaling": scaling_label(base), "vs_baseline": None,
             "dtype": "f32 storage, 3xTF32 tensor-core arithmetic (f32 accumulate)" if args.precision != "tf32"
                      else "f32 storage, single-pass TF32 arithmetic (reduced precision mode)",
             "data": "synthetic (seeded numpy default_rng: x~U[0,1), W~N(0,0.02), b~N(0,0.02), dy~N(0,1))"
-                    if wl.name == "c2" else "synthetic (seeded numpy default_rng, ~N(0,1))",
-            "config": {"workload": f"{base.name}: {base.desc}", "per_gpu": f"{wl.a_shape} x {wl.b_logical}",
-                       "parallelism": "single GPU" if world == 1 else
-                                      f"dp{world}: batch shard per rank" + (", NCCL reduce of dW" + ("+db" if wl.bias else "") + " overlapped with the dx GEMM"
-                                                                            if reduce_grads else ", replicas"),
-                       "precision": args.precision, "cuda_graph": graphed,
-                       "l2": (f"working set {ws:.0f} MB per step vs 126 MB L2, no flush" if ws > 126 else
-                              f"working set {ws:.0f} MB fits the 126 MB L2; not flushed between steps (stated)"),
-                       "flops_per_step_per_gpu": wl.flops},
+                    if wl.name == "c2" else "synthetic (seeded numpy default_rng, ~N(0,1); weight ~N(0,0.02))"
+                    if wl.name == "c4" else "synthetic (seeded numpy default_rng, ~N(0,1))",
+            "config": config_dict(base, world, args.precision),
+            "run": {"per_gpu": f"{wl.a_shape} x {wl.b_logical}", "cuda_graph": graphed, "shard_of": args.shard_of,
+                    "eager_ms_per_step": eager_ms, "flops_per_step_per_gpu": wl.flops},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "overlap": "3 streams, 2 device slots"},
             "gpu_launches": int(launches_per_step * args.steps),
             "clocks": clocks,
             "roofline": roofline,
+            "kernels": kernels,
         }
+        if timeline is not None:
+            line["timeline"] = timeline
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
@@ -543,9 +684,88 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_pointwise(args, F, base: Workload, dev, world: int, rank: int):
+    """The HBM-bound neighbours of the path: softmax forward+backward over the attention scores, and the
+    gradient-norm + clipped AdamW step that consumes dW.  Reported in GB/s of algorithmic bytes."""
+    import torch
+    T = F.DeviceTensor
+    rng = np.random.default_rng(rank)
+    peaks = load_peaks()
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    if base.kind == "softmax":
+        shape = base.a_shape
+        x = T.from_numpy(rng.standard_normal(shape, dtype=np.float32), dev)
+        dy = T.from_numpy(rng.standard_normal(shape, dtype=np.float32), dev)
+        y = F.softmax(x, -1)
+        n = int(np.prod(shape))
+        parts = [("softmax forward", lambda: F.softmax(x, -1), 8.0 * n),
+                 ("softmax backward", lambda: F.softmax_backward(dy, y, -1), 12.0 * n)]
+        host_in = {"x": x, "dy": dy}
+        outs = lambda: {"y": F.softmax(x, -1), "dx": F.softmax_backward(dy, F.softmax(x, -1), -1)}  # noqa: E731
+    else:
+        sizes = [768 * 3072, base.a_shape[0]]
+        ps = [T.from_numpy(rng.standard_normal(s, dtype=np.float32), dev) for s in sizes]
+        gs = [T.from_numpy(rng.standard_normal(s, dtype=np.float32), dev) for s in sizes]
+        ms = [T.from_numpy(np.zeros(s, np.float32), dev) for s in sizes]
+        vs = [T.from_numpy(np.zeros(s, np.float32), dev) for s in sizes]
+        sumsq = torch.zeros(1, dtype=torch.float64, device=dev)
+        lib = F._lib.lib()
+        from framework_b200.tensor import current_stream
+
+        def norm():
+            for i, g in enumerate(gs):
+                F._lib.check(lib.mni_b200_grad_sumsq(g.ptr, g.size, sumsq.data_ptr(), F._lib.ACCUMULATE_C if i else 0,
+                                                     current_stream()))
+
+        def step_all():
+            for p, m, v, g in zip(ps, ms, vs, gs):
+                F.adamw_step(p, m, v, g, lr=1e-3, weight_decay=0.01, step=3, grad_sumsq=sumsq, max_grad_norm=1.0,
+                             write_clipped_grad=False)
+        n = sum(sizes)
+        parts = [("gradient norm (f64 sum of squares)", norm, 4.0 * n),
+                 ("clipped AdamW step (param, m, v read+written, grad read)", step_all, 28.0 * n)]
+        host_in, outs = {}, None
+    kernels, total_ms, total_bytes = [], 0.0, 0.0
+    reps = max(5, min(args.steps, 100))
+    for label, fn, nbytes in parts:
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = F.launch_count()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms_ = e0.elapsed_time(e1) / reps
+        gbs = nbytes / (ms_ * 1e-3) / 1e9
+        kernels.append({"call": label, "us": round(ms_ * 1e3, 2), "launches": (F.launch_count() - l0) // reps,
+                        "gbs": round(gbs, 1), "algorithmic_bytes": nbytes, "bound": "hbm", "frac": round(gbs / hbm_peak, 4)})
+        total_ms += ms_
+        total_bytes += nbytes
+    F.device_status()
+    if rank != 0:
+        return
+    value = total_bytes / (total_ms * 1e-3) / 1e9
+    line = {"metric": f"{base.name}_algorithmic_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": reps,
+            "warmup": max(args.warmup, 3), "ms_per_step": total_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded numpy default_rng, ~N(0,1))",
+            "config": config_dict(base, world, "f32"),
+            "roofline": {"bound": "hbm", "achieved": value, "peak": hbm_peak, "unit": "GB/s", "frac": value / hbm_peak,
+                         "traffic": None, "kernel": "all calls of the workload, back to back",
+                         "peak_source": "measured hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650"},
+            "kernels": kernels, "gpu_launches": int(sum(k["launches"] for k in kernels) * reps)}
+    if not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline_pointwise(base)
+    print(json.dumps(line), flush=True)
+
+
 def working_set_mb(wl: Workload) -> float:
     if wl.kind == "attention":
         elems = 2 * np.prod(wl.out_shape) + 8 * np.prod(wl.a_shape)
+    elif wl.kind in ("softmax", "adamw"):
+        elems = 4 * np.prod(wl.a_shape)
     else:
         elems = 2 * np.prod(wl.a_shape) + 2 * np.prod(wl.b_shape) + 2 * np.prod(wl.out_shape)
     return float(elems) * 4 / 1e6
@@ -594,10 +814,24 @@ def host_threads() -> int:
         return os.cpu_count() or 1
 
 
+def cpu_rate_gflops(O, threads: int) -> float:
+    """Quick calibration of the CPU loop's speed (a 512 x 512 x 2048 product per thread) so that samples can be
+    sized in seconds rather than in flops."""
+    m = 512 * max(threads, 1)
+    rng = np.random.default_rng(1)
+    a = O.HostTensor.from_array(rng.standard_normal((m, 512), dtype=np.float32))
+    b = O.HostTensor.from_array(rng.standard_normal((512, 2048), dtype=np.float32))
+    O.matmul(a, b, threads=threads)
+    t0 = time.perf_counter()
+    O.matmul(a, b, threads=threads)
+    return 2.0 * m * 512 * 2048 / (time.perf_counter() - t0) / 1e9
+
+
 def cpu_baseline_sample(wl: Workload, threads: int) -> dict:
     import oracle as O
     O.build()
-    small, what = cpu_sample_workload(wl, budget_gflop=120.0 * max(threads, 1))
+    rate = cpu_rate_gflops(O, threads)
+    small, what = cpu_sample_workload(wl, budget_gflop=max(1.0, 12.0 * rate))     # about 12 s of CPU work
     tens = cpu_tensors(O, small)
     t0 = time.perf_counter()
     cpu_step(O, small, tens, threads)
@@ -605,6 +839,32 @@ def cpu_baseline_sample(wl: Workload, threads: int) -> dict:
     return {"value": small.flops / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
             "sample": f"{what}; {small.flops / 1e9:.1f} GFLOP in {dt:.2f} s; C restatement of the reference's "
                       f"single-threaded CPU backend (gcc -O3 -ffp-contract=off)",
+            "host_cores": host_threads()}
+
+
+def cpu_baseline_pointwise(base: Workload) -> dict:
+    import oracle as O
+    O.build()
+    rng = np.random.default_rng(0)
+    if base.kind == "softmax":
+        shape = (2,) + tuple(base.a_shape[1:])                       # 2 of the 8 batches
+        x = rng.standard_normal(shape, dtype=np.float32)
+        dy = rng.standard_normal(shape, dtype=np.float32)
+        t0 = time.perf_counter()
+        y = O.softmax(x, -1)
+        O.softmax_backward(dy, y, -1)
+        dt = time.perf_counter() - t0
+        nbytes, what = 20.0 * x.size, "2/8 of the batches, forward + backward"
+    else:
+        n = 16 * 1024 * 1024
+        p, g = rng.standard_normal(n, dtype=np.float32), rng.standard_normal(n, dtype=np.float32)
+        m, v = np.zeros(n, np.float32), np.zeros(n, np.float32)
+        t0 = time.perf_counter()
+        O.clip_and_step([p], [m], [v], [g], lr=1e-3, weight_decay=0.01, step=3, max_grad_norm=1.0)
+        dt = time.perf_counter() - t0
+        nbytes, what = 32.0 * n, "16 M elements, norm + clip + AdamW"
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": f"{what}; {dt:.2f} s; C restatement of the reference's single-threaded CPU backend",
             "host_cores": host_threads()}
 
 
@@ -617,12 +877,21 @@ def run_reference(args):
     O.build()
     threads = host_threads()      # not OMP_NUM_THREADS: launchers set that to 1
     wl = WORKLOADS[args.workload]
-    small, what = cpu_sample_workload(wl, budget_gflop=14.0 * threads)
+    if wl.kind in ("softmax", "adamw"):
+        cpu = cpu_baseline_pointwise(wl)
+        print(json.dumps({"impl": "reference", "metric": f"{wl.name}_algorithmic_gbs", "value": cpu["value"], "unit": "GB/s",
+                          "n_gpus": world, "steps": 1, "warmup": 0, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(wl, world, "f32"),
+                          "cpu_baseline": cpu, "e2e": {"value": cpu["value"], "unit": "GB/s", "h2d_bytes_per_step": 0,
+                                                       "d2h_bytes_per_step": 0}}), flush=True)
+        return
+    # Size the per-step sample so that all warm-up and timed steps together take about 90 s of CPU time.
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    rate = cpu_rate_gflops(O, threads)
+    small, what = cpu_sample_workload(wl, budget_gflop=max(0.5, 90.0 / (steps + warm) * rate))
     tens = cpu_tensors(O, small)
-    warm = min(args.warmup, 1)
     for _ in range(warm):
         cpu_step(O, small, tens, threads)
-    steps = max(1, min(args.steps, 5))
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_step(O, small, tens, threads)
@@ -632,9 +901,10 @@ def run_reference(args):
               f"single-threaded, this run spreads its row loop over {threads} threads (bit-identical results)")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
-        "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic (seeded numpy default_rng)",
-        "config": {"workload": f"{wl.name}: {wl.desc}", "parallelism": f"CPU, {threads} threads"},
+        "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": scaling_label(wl),
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded numpy default_rng)",
+        "config": config_dict(wl, world, args.precision),
+        "run": {"threads": threads, "calibrated_gflops": round(rate, 1)},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -644,14 +914,16 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: only for steps under 0.2 ms)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="with one GPU: run rank 0's shard of an N-rank job (c4 / c5a), without the reduce")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-from .build import LIB_PATH
+from .build import LIB_PATH, source_hash
 
 MAX_DIMS = 8
 
@@ -49,6 +49,7 @@ _lib = None
 
 _SIGNATURES = {
     "mni_b200_version": (C.c_int, []),
+    "mni_b200_build_id": (C.c_char_p, []),
     "mni_b200_last_error": (C.c_char_p, []),
     "mni_b200_matmul_fwd": (C.c_int, [C.POINTER(View), C.POINTER(View), C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "mni_b200_matmul_bias_gelu_fwd": (C.c_int, [C.POINTER(View), C.POINTER(View), C.c_void_p, C.c_void_p, C.c_void_p,
@@ -84,7 +85,8 @@ def exported_symbols() -> list:
 
 
 def lib() -> C.CDLL:
-    """Loads the in-tree shared library (raises if it has not been built)."""
+    """Loads the in-tree shared library.  Raises if it has not been built, or if it was built from
+    sources that differ from the tree's (the library carries a hash of its sources)."""
     global _lib
     if _lib is None:
         if not os.path.exists(LIB_PATH):
@@ -96,6 +98,11 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)
             fn.restype = res
             fn.argtypes = args
+        built_from = handle.mni_b200_build_id().decode()
+        if built_from != source_hash():
+            raise ImportError(
+                f"{LIB_PATH} was built from other sources than the ones in csrc/ and include/ "
+                "(rebuild it with `python -m framework_b200.build`); refusing to run a stale library")
         _lib = handle
     return _lib
 

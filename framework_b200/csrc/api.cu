@@ -43,6 +43,21 @@ DeviceState g_dev[kMaxDevices];
 
 int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
+// x^n in f32 the way Rust's f32::powi evaluates it (ops/optimizer.rs:26-27 call it for the bias corrections):
+// binary exponentiation from the lowest exponent bit up -- multiply the result in when the bit is set,
+// square the base between bits -- every product rounded to f32.  O(log n) and, from n = 4 on, rounded
+// differently from n successive multiplications.
+float powi_f32(float x, uint32_t n) {
+    float r = 1.0f;
+    while (true) {
+        if (n & 1u) r *= x;
+        n >>= 1;
+        if (n == 0) break;
+        x *= x;
+    }
+    return r;
+}
+
 // Largest M*N*K*batch for which the two gradient products of a backward call are issued side by side.
 double overlap_work_limit() {
     const char *v = getenv("MNI_B200_BWD_OVERLAP_WORK");
@@ -79,6 +94,9 @@ int device_state(DeviceState **out) {
     if (e != cudaSuccess) return fail(MNI_B200_ERR_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
     if (dev < 0 || dev >= kMaxDevices) return fail(MNI_B200_ERR_DEVICE, "device ordinal %d out of range", dev);
     DeviceState &st = g_dev[dev];
+    // First use of a device: under the device's lock, so that two host threads that make their first
+    // call together initialise it once (init is only ever read or written with the lock held).
+    std::lock_guard<std::mutex> lock(st.mu);
     if (!st.init) {
         cudaDeviceProp prop;
         e = cudaGetDeviceProperties(&prop, dev);
@@ -95,9 +113,9 @@ int device_state(DeviceState **out) {
         st.err_word = static_cast<unsigned int *>(p);
         e = cudaMemset(st.err_word, 0, sizeof(unsigned int));
         if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "cudaMemset: %s", cudaGetErrorString(e));
-        e = cudaStreamCreateWithFlags(&st.side, cudaStreamNonBlocking);
-        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&st.ev_fork, cudaEventDisableTiming);
-        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&st.ev_join, cudaEventDisableTiming);
+        if (!st.side) e = cudaStreamCreateWithFlags(&st.side, cudaStreamNonBlocking);
+        if (e == cudaSuccess && !st.ev_fork) e = cudaEventCreateWithFlags(&st.ev_fork, cudaEventDisableTiming);
+        if (e == cudaSuccess && !st.ev_join) e = cudaEventCreateWithFlags(&st.ev_join, cudaEventDisableTiming);
         if (e != cudaSuccess) return fail(MNI_B200_ERR_CUDA, "side stream set-up: %s", cudaGetErrorString(e));
         st.init = true;
     }
@@ -224,6 +242,7 @@ struct Call {
     cudaStream_t stream;
     uint32_t flags;
     uint8_t *base = nullptr;   // resolved scratch base (real mode, second pass)
+    int flag_bank = 0;         // 1 while launches go to the library's side stream
     bool dry() const { return arena.dry; }
     float *at(size_t off) const { return reinterpret_cast<float *>(base + off); }
 };
@@ -261,6 +280,7 @@ int make_operand(Call &c, const mni_b200_view &v, bool transposed, Operand &op) 
 int run_gemm(Call &c, GemmProblem &p) {
     p.fast_tf32 = (c.flags & MNI_B200_PRECISION_TF32) != 0;
     p.force_splits = static_cast<int>((c.flags >> 16) & 0xffu);
+    p.flag_bank = c.flag_bank;
     if (p.M > 0x7fffffffLL || p.N > 0x7fffffffLL || p.K > 0x7fffffffLL || p.batch * p.fold > 0x7fffffffLL ||
         p.batch * ((p.M + 127) / 128) * ((p.N + 63) / 64) > 0x3fffffffLL)
         return fail(MNI_B200_ERR_TOO_LARGE, "GEMM %lld x %lld x %lld (batch %lld) exceeds the kernels' int32 indexing",
@@ -474,6 +494,7 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
     struct Join {      // joins the side stream on every exit path once it has been forked
         Call &c; cudaStream_t main; bool on;
         ~Join() {
+            c.flag_bank = 0;
             if (!on) return;
             c.stream = main;
             if (cudaEventRecord(c.st->ev_join, c.st->side) == cudaSuccess) cudaStreamWaitEvent(main, c.st->ev_join, 0);
@@ -552,7 +573,7 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
     }
 
     // grad_b = unbroadcast(a^T . dc, b.shape)   (ops/matmul.rs:242-251)
-    if (overlap) c.stream = c.st->side;
+    if (overlap) { c.stream = c.st->side; c.flag_bank = 1; }
     if (db && b_elems > 0) {
         if (s.M == 0 || g_batch == 0) {
             rc = zero_or_bias_fill(c, db, b_elems, 1, nullptr, acc_db);
@@ -608,6 +629,18 @@ int with_scratch(uint32_t flags, void *stream, Body body) {
 }
 
 }  // namespace
+
+int device_sm_count() {
+    static std::atomic<int> cache[kMaxDevices];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    int n = cache[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cache[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
 
 bool pdl_enabled() {
     static const bool on = env_flag("MNI_B200_PDL", 1);
@@ -767,9 +800,8 @@ int mni_b200_adamw_step(float *param, float *m, float *v, float *grad, int64_t n
     DeviceState *st = nullptr;
     int rc = device_state(&st);
     if (rc) return rc;
-    // bias corrections of ops/optimizer.rs:31-32: 1 - beta^step in f32
-    float p1 = 1.0f, p2 = 1.0f;
-    for (uint32_t i = 0; i < step; ++i) { p1 *= beta1; p2 *= beta2; }
+    // bias corrections of ops/optimizer.rs:26-27: 1 - beta.powi(step) in f32
+    const float p1 = powi_f32(beta1, step), p2 = powi_f32(beta2, step);
     return launch_adamw(param, m, v, grad, n, lr, beta1, beta2, eps, weight_decay, 1.0f - p1, 1.0f - p2, grad_sumsq,
                         max_grad_norm, write_clipped_grad != 0, static_cast<cudaStream_t>(stream));
 }
@@ -805,7 +837,9 @@ int mni_b200_workspace_query(const mni_b200_view *a, const mni_b200_view *b, uin
     Shapes s;
     rc = analyse(a, b, s);
     if (rc) return rc;
-    // The forward output's gradient: contiguous, broadcast batch + [M, N].
+    // The forward output's gradient, broadcast batch + [M, N], in the two forms that bound what a real one can
+    // need: contiguous and 256-byte aligned (read in place), and a view no descriptor covers (neither matrix
+    // dim has unit stride), which is gathered into scratch once for each of its three uses.
     mni_b200_view dc{};
     dc.ptr = reinterpret_cast<const float *>(static_cast<uintptr_t>(256));
     dc.ndim = s.out_nb + 2;
@@ -813,16 +847,33 @@ int mni_b200_workspace_query(const mni_b200_view *a, const mni_b200_view *b, uin
     dc.shape[s.out_nb] = s.M; dc.shape[s.out_nb + 1] = s.N;
     int64_t acc = 1;
     for (int d = dc.ndim - 1; d >= 0; --d) { dc.stride[d] = acc; acc *= dc.shape[d]; }
+    mni_b200_view dc_strided = dc;
+    for (int d = 0; d < dc.ndim; ++d) dc_strided.stride[d] = dc.stride[d] * 2;
     float *fake = reinterpret_cast<float *>(static_cast<uintptr_t>(256));
-    Call c1;
-    c1.st = st; c1.arena.dry = true; c1.stream = nullptr; c1.flags = flags;
-    rc = fwd_body(c1, a, b, fake, nullptr);
+    size_t need = 0;
+    auto dry = [&](auto body) -> int {
+        Call c;
+        c.st = st; c.arena.dry = true; c.stream = nullptr; c.flags = flags;
+        const int r = body(c);
+        need = std::max(need, c.arena.used);
+        return r;
+    };
+    rc = dry([&](Call &c) { return fwd_body(c, a, b, fake, nullptr); });
     if (rc) return rc;
-    Call c2;
-    c2.st = st; c2.arena.dry = true; c2.stream = nullptr; c2.flags = flags;
-    rc = bwd_body(c2, a, b, &dc, fake, fake, fake);
+    rc = dry([&](Call &c) { return bwd_body(c, a, b, &dc, fake, fake, fake); });
     if (rc) return rc;
-    *bytes = std::max(c1.arena.used, c2.arena.used);
+    rc = dry([&](Call &c) { return bwd_body(c, a, b, &dc_strided, fake, fake, fake); });
+    if (rc) return rc;
+    // bias + GELU forward without a `pre` output: when the epilogue cannot be fused the product needs a temporary
+    rc = dry([&](Call &c) { return fwd_gelu_body(c, a, b, fake, nullptr, fake); });
+    if (rc) return rc;
+    // the pointwise entry points on the forward output: column-sum partials, gradient-norm partials
+    const int64_t rows = s.batch * s.M;
+    need = std::max(need, (colsum_partial_bytes(std::max<int64_t>(rows, 1), std::max<int64_t>(s.N, 1), st->sm_count) + 255) &
+                              ~static_cast<size_t>(255));
+    const int64_t biggest = std::max({s.a_batch * s.M * s.K, s.b_batch * s.K * s.N, rows * s.N, int64_t{1}});
+    need = std::max(need, (sumsq_partial_bytes(biggest, st->sm_count) + 255) & ~static_cast<size_t>(255));
+    *bytes = need;
     return MNI_B200_OK;
 }
 

@@ -36,8 +36,11 @@
 // drain to the common exit, where TMEM is released.  Nothing traps.
 #include "internal.h"
 
+#include <string.h>
+
 #include <algorithm>
 #include <mutex>
+#include <unordered_map>
 
 namespace mni {
 
@@ -49,7 +52,7 @@ constexpr int kSkMaxShare = 6;                             // balanced tail: mos
 constexpr int kEpiWarps = 8;                                // two per TMEM lane quarter, half of the columns each
 constexpr int kEpiBufBytes = 32 * 128;                     // one 32 x 32 f32 patch
 constexpr int kBarBytes = (3 * kMaxStages + 4) * 8 + 16;
-constexpr long long kWaitCycles = 4000000000LL;            // ~2 s at 2 GHz
+constexpr long long kWaitCycles = 4000000000LL;            // default limit of every device-side wait: ~2 s at 2 GHz
 
 enum OperandMode { kKMajor = 0, kMnMultiBox = 1, kMnSingleBox = 2 };
 enum EpilogueMode { kEpiPlainStores = 0, kEpiTmaStore = 1, kEpiTmaReduce = 2, kEpiVectorStores = 3 };
@@ -104,6 +107,8 @@ struct KParams {
     FastDiv fd_splits, fd_per_batch, fd_group_sz, fd_group_m, fd_last_gm;   // decode_unit
     FastDiv fd_a_cnt, fd_a_d1, fd_a_d2, fd_b_cnt, fd_b_d1, fd_b_d2;         // batch_coords
     unsigned int *err;
+    long long wait_cycles;     // limit of every bounded wait in clock cycles (kWaitCycles unless a test shortens it)
+    int withhold_at;           // test hook: the producer arms its n-th k-block (1-based) but issues no copy for it; 0 = off
     unsigned long long *prof;  // optional role wait counters (null = off)
     // Balanced tail ("stream-K"): tiles [sk_first_tile, tiles) are not dealt out whole; their k-blocks are
     // cut into one contiguous range per CTA (pair), so a ragged last wave costs its share, not a full wave.
@@ -143,7 +148,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // the time the first try_wait is suspended by the hardware); without it the satisfied case costs one
 // try_wait and no clock reads.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          unsigned int *err, uint32_t code, long long &waited, bool timed) {
+                                          unsigned int *err, uint32_t code, long long &waited, bool timed,
+                                          long long limit) {
     long long t0 = 0;
     if (timed) t0 = clock64();
     if (mbar_try_wait(bar, parity)) {
@@ -159,7 +165,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
         if ((++spins & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitCycles) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1u;
                 atomicCAS(err, 0u, code);
                 return false;
@@ -169,8 +175,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 // Warp-collective form: every lane polls, the verdict is made uniform.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                               unsigned int *err, uint32_t code, long long &waited, bool timed) {
-    const bool ok = mbar_wait(bar, parity, abort_flag, err, code, waited, timed);
+                                               unsigned int *err, uint32_t code, long long &waited, bool timed,
+                                               long long limit) {
+    const bool ok = mbar_wait(bar, parity, abort_flag, err, code, waited, timed, limit);
     return __all_sync(0xffffffffu, ok);
 }
 // Non-blocking look at a barrier phase (try_wait may suspend the thread; this never does).
@@ -543,16 +550,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const int rowA = t.tm * (BM * CG) + static_cast<int>(cta_rank) * BM;
                 const int rowB = t.tn * BN + static_cast<int>(cta_rank) * BNL;
                 for (int it = t.it0; it < t.it1; ++it) {
-                    ok = mbar_wait_warp(bar_empty + 8u * stage, phase ^ 1u, abort_flag, p.err, 0x100u | stage, waited, timed);
+                    ok = mbar_wait_warp(bar_empty + 8u * stage, phase ^ 1u, abort_flag, p.err, 0x100u | stage, waited, timed, p.wait_cycles);
                     if (!ok) break;
                     const uint32_t full = bar_full + 8u * stage;
                     const int k0 = kk * BK;
+                    ++armed;
                     if (elect_one()) {
                         mbar_arrive_expect_tx(full, RAW_BYTES);
-                        load_operand(p.a_mode, dstA, &tmA, full, k0, rowA, BM / 32, CHUNK_BYTES, a0, a1, a2);
-                        load_operand(p.b_mode, dstA + A_BYTES, &tmB, full, k0, rowB, BNL / 32, CHUNK_BYTES, b0, b1, b2);
+                        if (armed != p.withhold_at) {        // test hook: a stage that is armed and never filled
+                            load_operand(p.a_mode, dstA, &tmA, full, k0, rowA, BM / 32, CHUNK_BYTES, a0, a1, a2);
+                            load_operand(p.b_mode, dstA + A_BYTES, &tmB, full, k0, rowB, BNL / 32, CHUNK_BYTES, b0, b1, b2);
+                        }
                     }
-                    ++armed;
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; dstA = dstA0; } else { dstA += STAGE_BYTES; }
                     if (++kk == p.kiters) {
                         kk = 0;
@@ -570,7 +579,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int i = 0; i < pending; ++i) {
                     if (--stage < 0) { stage = p.stages - 1; phase ^= 1u; }
                     const long long t0 = clock64();
-                    while (!mbar_try_wait(bar_full + 8u * stage, phase) && clock64() - t0 < kWaitCycles / 8) {}
+                    while (!mbar_try_wait(bar_full + 8u * stage, phase) && clock64() - t0 < p.wait_cycles / 8) {}
                 }
             }
             if (p.prof && lane == 0) atomicAdd(p.prof + 0, static_cast<unsigned long long>(waited));
@@ -602,14 +611,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const int iters = wt.it1 - wt.it0;
                 const int buf = acc_it & 1;
                 const uint32_t acc_phase = (acc_it >> 1) & 1;
-                ok = mbar_wait_warp(bar_acc_empty + 8u * buf, acc_phase ^ 1u, abort_flag, p.err, 0x200u | buf, waited_acc, timed);
+                ok = mbar_wait_warp(bar_acc_empty + 8u * buf, acc_phase ^ 1u, abort_flag, p.err, 0x200u | buf, waited_acc, timed, p.wait_cycles);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
                 uint32_t accumulate = 0;
                 for (int it = 0; it < iters; ++it) {
                     if (!next_ready) {
-                        ok = mbar_wait_warp(ready0 + 8u * stage, phase, abort_flag, p.err, 0x300u | stage, waited, timed);
+                        ok = mbar_wait_warp(ready0 + 8u * stage, phase, abort_flag, p.err, 0x300u | stage, waited, timed, p.wait_cycles);
                         if (!ok) break;
                     }
                     tc_fence_after();
@@ -687,7 +696,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             while (ok && work_next(p, wi, wt)) {
                 const int iters = wt.it1 - wt.it0;
                 for (int it = 0; it < iters; ++it) {
-                    ok = mbar_wait(bar_full + 8u * stage, phase, abort_flag, p.err, 0x400u | stage, waited, timed);
+                    ok = mbar_wait(bar_full + 8u * stage, phase, abort_flag, p.err, 0x400u | stage, waited, timed, p.wait_cycles);
                     if (!ok) break;
                     if constexpr (TA) {
                         // A: this thread owns row (lane quarter of its warp) and 16 of the 32 k columns.
@@ -782,7 +791,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         while (ok && work_next(p, wi, t)) {
             const int buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
-            ok = mbar_wait(bar_acc_full + 8u * buf, acc_phase, abort_flag, p.err, 0x500u | buf, waited, timed);
+            ok = mbar_wait(bar_acc_full + 8u * buf, acc_phase, abort_flag, p.err, 0x500u | buf, waited, timed, p.wait_cycles);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -863,7 +872,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                 while (true) {
                                     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
                                     if (seen != 0u) break;
-                                    if (*abort_flag || clock64() - tw0 > kWaitCycles) {
+                                    if (*abort_flag || clock64() - tw0 > p.wait_cycles) {
                                         *abort_flag = 1u;
                                         atomicCAS(p.err, 0u, 0x600u);
                                         ok = false;
@@ -1163,12 +1172,50 @@ int env_int(const char *name, int dflt) {
     return v && *v ? atoi(v) : dflt;
 }
 
+// Encoded tensor maps are a pure function of (pointer, extents, strides, box, swizzle): a training loop calls with
+// the same handful of buffers every step, so each host thread keeps the maps it has built (bounded; dropped
+// wholesale when full) and an eager call pays a hash lookup instead of three or four driver encodes.
+struct MapKey {
+    const void *ptr;
+    cuuint64_t dims[5];
+    cuuint64_t strides[4];
+    cuuint32_t box[5];
+    int swz;
+    bool operator==(const MapKey &o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const {
+        const unsigned char *b = reinterpret_cast<const unsigned char *>(&k);
+        uint64_t h = 1469598103934665603ull;            // FNV-1a over the key's bytes
+        for (size_t i = 0; i < sizeof(MapKey); ++i) { h ^= b[i]; h *= 1099511628211ull; }
+        return static_cast<size_t>(h);
+    }
+};
+constexpr size_t kMapCacheEntries = 512;
+
 CUresult encode(CUtensorMap *map, const float *ptr, const cuuint64_t *dims, const cuuint64_t *strides,
                 const cuuint32_t *box, CUtensorMapSwizzle swz) {
+    static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static const bool use_cache = env_int("MNI_B200_MAP_CACHE", 1) != 0;
+    MapKey key;
+    memset(&key, 0, sizeof(key));                       // padding bytes take part in the comparison
+    key.ptr = ptr;
+    for (int i = 0; i < 5; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+    for (int i = 0; i < 4; ++i) key.strides[i] = strides[i];
+    key.swz = static_cast<int>(swz);
+    if (use_cache) {
+        auto it = cache.find(key);
+        if (it != cache.end()) { *map = it->second; return CUDA_SUCCESS; }
+    }
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(ptr), dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(ptr), dims, strides, box,
+                                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS && use_cache) {
+        if (cache.size() >= kMapCacheEntries) cache.clear();
+        cache.emplace(key, *map);
+    }
+    return r;
 }
 
 // Builds the tensor map of one operand and reports the OperandMode the kernel must use for it.
@@ -1352,10 +1399,15 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     // boundary are summed in the owner's epilogue, in slot order).
     pl.sk = false;
     pl.sk_first_tile = 0;
-    if (splits == 1 && p.D == nullptr && env_int("MNI_B200_STREAMK", 0) != 0) {
+    // MNI_B200_STREAMK: unset = on when the whole-tile schedule would idle more than a fifth of the slot-rounds
+    // (measured: below that the idle SMs of a ragged wave are power headroom for the busy ones at the 1 kW cap
+    // and the balanced tail does not pay); 1 = on from 8 % idle; 0 = never.
+    const int sk_env = env_int("MNI_B200_STREAMK", -1);
+    if (splits == 1 && p.D == nullptr && sk_env != 0) {
         const long long full_rounds = tiles / slots, rem = tiles - full_rounds * slots;
         const double eff = static_cast<double>(tiles) / static_cast<double>((full_rounds + 1) * slots);
-        if (rem > 0 && eff < 0.92 && iters >= 8 && tiles * 2 > slots) {
+        const double eff_limit = sk_env > 0 ? 0.92 : 0.80;
+        if (rem > 0 && eff < eff_limit && iters >= 8 && tiles * 2 > slots) {
             // the tail takes one whole round along when there is one, so that a range is at least a tile long
             const long long whole = full_rounds > 0 ? full_rounds - 1 : 0;
             const long long range = (tiles - whole * slots) * iters / slots;
@@ -1410,7 +1462,8 @@ cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtenso
 // is parked, and per region of a tail tile a ticket; the unit that reduces a tile clears what it used, so the
 // array is all zero between launches.
 constexpr int kSkFlagCount = 3 * 256 * kEpiWarps;
-__device__ unsigned int g_sk_flags[kSkFlagCount];
+constexpr int kSkFlagBanks = 2;            // bank 1 serves the launches a backward call puts on the library's side stream
+__device__ unsigned int g_sk_flags[kSkFlagBanks * kSkFlagCount];
 
 unsigned int *sk_flags_ptr() {
     static thread_local int cached_dev = -1;
@@ -1583,6 +1636,14 @@ int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, in
     k.bias = p.bias;
     k.accumulate = p.accumulate;
     k.err = err_word;
+    {
+        // Tests shorten the limit of the device-side waits; the withhold hook (a stage that never fills, so
+        // that the waits do run out) is honoured only together with a limit of at most ~0.1 s.
+        const char *w = getenv("MNI_B200_WAIT_CYCLES");
+        const long long wc = w && *w ? atoll(w) : 0;
+        k.wait_cycles = wc > 0 ? wc : kWaitCycles;
+        k.withhold_at = k.wait_cycles <= 200000000LL ? env_int("MNI_B200_TEST_WITHHOLD_KBLOCK", 0) : 0;
+    }
     k.prof = env_int("MNI_B200_ROLE_WAITS", 0) ? role_wait_ptr() : nullptr;
     k.sk = pl.sk ? 1 : 0;
     k.sk_first_tile = pl.sk_first_tile;
@@ -1591,6 +1652,7 @@ int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, in
     if (pl.sk) {
         k.sk_flags = sk_flags_ptr();
         if (!k.sk_flags) return fail(MNI_B200_ERR_CUDA, "balanced-tail flags unavailable");
+        k.sk_flags += (p.flag_bank > 0 ? 1 : 0) * kSkFlagCount;
         // ready flags for 2 parking places per CTA, then one ticket per region of a tail tile (fewer tiles than CTAs)
         if (pl.grid * 3 * kEpiWarps > kSkFlagCount) return fail(MNI_B200_ERR_CUDA, "balanced-tail flag array too small");
     }

@@ -50,6 +50,7 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 // error plumbing
 // ---------------------------------------------------------------------------
 int fail(int status, const char *fmt, ...);          // records the thread-local message, returns status
+int device_sm_count();                                // SM count of the current device (cached per device)
 extern std::atomic<uint64_t> g_launches;              // kernels launched by this library
 
 #define MNI_CUDA(call)                                                                   \
@@ -94,6 +95,7 @@ struct GemmProblem {
     bool accumulate = false;       // C += ...
     bool fast_tf32 = false;        // one TF32 pass instead of the 3-pass split
     int force_splits = 0;          // tests
+    int flag_bank = 0;             // 1 for launches on the library's side stream: their own set of balanced-tail flags
     // Optional second output D = gelu(C + bias) written by the same epilogue (C itself is skipped if null).
     float *D = nullptr;
 };

@@ -10,9 +10,9 @@ namespace {
 
 constexpr int kMaxDims = MNI_B200_MAX_DIMS;
 
-int grid_for(long long work_items, int threads, int sm_count_hint = 148) {
+int grid_for(long long work_items, int threads) {
     const long long blocks = (work_items + threads - 1) / threads;
-    return static_cast<int>(std::max<long long>(1, std::min<long long>(blocks, sm_count_hint * 16LL)));
+    return static_cast<int>(std::max<long long>(1, std::min<long long>(blocks, device_sm_count() * 16LL)));
 }
 
 // out[r, j] = y[r, j] + bias[j]; one float4 per thread-iteration when n % 4 == 0.

@@ -686,7 +686,7 @@ int launch_skinny_dw(const float *x, int64_t ldx, const float *dy, int64_t lddy,
                      bool accumulate, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
     const int mt = pick_mt(M);
     const int strips = static_cast<int>((N + 4 * kSkinnyThreads - 1) / (4 * kSkinnyThreads));
-    long long slabs = std::max<long long>(1, (148 * 8LL) / strips);
+    long long slabs = std::max<long long>(1, (device_sm_count() * 8LL) / strips);
     long long k_per = std::max<long long>(8, (K + slabs - 1) / slabs);
     k_per = std::min<long long>(k_per, 1024);
     slabs = (K + k_per - 1) / k_per;

@@ -98,6 +98,16 @@ class DeviceTensor:
             raise ValueError(f"invalid permutation {list(dims)}")
         return DeviceTensor(self.storage, [self.shape[d] for d in dims], [self.strides[d] for d in dims])
 
+    def narrow(self, dim: int, start: int, length: int) -> "DeviceTensor":
+        """The sub-tensor [start, start + length) of dimension `dim`, as a view of the same storage (pointer
+        offset + same strides): how row or column panels of an operand reach the kernels without a copy."""
+        d = dim + self.ndim if dim < 0 else dim
+        if not (0 <= d < self.ndim and 0 <= start and length >= 0 and start + length <= self.shape[d]):
+            raise ValueError(f"narrow({dim}, {start}, {length}) out of range for shape {self.shape}")
+        shape = list(self.shape)
+        shape[d] = length
+        return DeviceTensor(self.storage[start * self.strides[d]:], shape, self.strides)
+
     def contiguous(self) -> "DeviceTensor":
         """ops/layout.rs:218-231 / tensor.rs:510-517, done on the device."""
         if self.is_contiguous():

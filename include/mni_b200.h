@@ -23,6 +23,15 @@
  *     expects (ops/matmul.rs:145, :211, :218).
  *   - No cuBLAS, no CPU fallback: if the device is not sm_100 the calls fail
  *     with MNI_B200_ERR_DEVICE.
+ *   - Threads and streams.  Calls may come from any host thread; state is per
+ *     device and guarded by a per-device lock.  The scratch buffer, the finish
+ *     tickets of the split-K / streaming kernels and the flags of the balanced
+ *     tail are ONE set per device, shared by every stream: two calls whose
+ *     kernels can run at the same time on one device (different streams with no
+ *     event between them) race on them.  Keep a device's calls on one stream --
+ *     what the reference does (device.rs:37) -- or order the streams with events.
+ *     The library's own side stream is forked from and joined to the caller's
+ *     stream inside one call and never overlaps the next call's kernels.
  */
 #ifndef MNI_B200_H
 #define MNI_B200_H
@@ -77,6 +86,10 @@ typedef enum mni_b200_status {
 
 /* Library version: major*10000 + minor*100 + patch. */
 MNI_B200_API int mni_b200_version(void);
+
+/* sha256 (hex) of the source files this binary was built from, so that a loader can refuse a stale build.
+ * (No counterpart in the reference.) */
+MNI_B200_API const char *mni_b200_build_id(void);
 
 /* Message of the calling thread's most recent failing call ("" if none). */
 MNI_B200_API const char *mni_b200_last_error(void);
@@ -220,7 +233,13 @@ MNI_B200_API int mni_b200_contiguous(const mni_b200_view *src, float *dst, void 
  * device.  mni_b200_workspace_set hands it a caller-owned buffer instead
  * (bytes == 0 / ptr == NULL returns to the library-owned one); calls then fail
  * with MNI_B200_ERR_WORKSPACE rather than allocate.  mni_b200_workspace_query
- * returns the bytes the given forward+backward problem may need.
+ * returns an upper bound, for operands a and b as given (their strides and
+ * alignment count), over: mni_b200_matmul_fwd; mni_b200_matmul_bias_gelu_fwd
+ * with or without a `pre` output; mni_b200_matmul_bwd with da, db and dbias and
+ * ANY view of the output gradient (contiguous, or strided so that it has to be
+ * gathered first); and the pointwise entry points (add_bias_bwd, bias_gelu_bwd,
+ * grad_sumsq) applied to tensors no larger than a, b or the forward output.
+ * The flags given are the flags the later calls must use.
  */
 MNI_B200_API int mni_b200_workspace_set(void *ptr, size_t bytes);
 MNI_B200_API int mni_b200_workspace_query(const mni_b200_view *a, const mni_b200_view *b, uint32_t flags,

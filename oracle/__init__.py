@@ -7,5 +7,5 @@ never does.
 from .oracle import (  # noqa: F401
     HostTensor, build, lib, matmul, matmul_backward, add, add_backward,
     permute, permute_backward, contiguous, max_threads, matmul_contig_raw, bias_gelu, bias_gelu_backward, adamw_step, grad_norm, clip_and_step,
-    softmax, softmax_backward,
+    softmax, softmax_backward, powi,
 )

@@ -368,13 +368,25 @@ void oracle_softmax_bwd(const float *grad, const float *sm, float *out, int64_t 
         }
 }
 
+/* f32::powi as the reference's build evaluates it (ops/optimizer.rs:26-27): binary exponentiation,
+ * lowest exponent bit first, each product rounded to f32. */
+float oracle_powi(float x, int n) {
+    float r = 1.0f;
+    unsigned int e = n < 0 ? 0u - (unsigned int)n : (unsigned int)n;
+    for (;;) {
+        if (e & 1u) r *= x;
+        e >>= 1;
+        if (e == 0) break;
+        x *= x;
+    }
+    return n < 0 ? 1.0f / r : r;
+}
+
 /* ops/optimizer.rs:22-65  AdamW on one parameter, CPU backend: decoupled decay first (only if
- * weight_decay > 0), then the moment updates and the bias-corrected step.  bc = 1 - beta^step. */
+ * weight_decay > 0), then the moment updates and the bias-corrected step.  bc = 1 - beta.powi(step). */
 void oracle_adamw_step(float *data, float *m, float *v, const float *grad, int64_t n, float lr, float beta1,
                        float beta2, float eps, float weight_decay, int step) {
-    float p1 = 1.0f, p2 = 1.0f;
-    for (int i = 0; i < step; ++i) { p1 *= beta1; p2 *= beta2; }
-    const float bc1 = 1.0f - p1, bc2 = 1.0f - p2;
+    const float bc1 = 1.0f - oracle_powi(beta1, step), bc2 = 1.0f - oracle_powi(beta2, step);
     for (int64_t i = 0; i < n; ++i) {
         const float g = grad[i];
         if (weight_decay > 0.0f) data[i] *= 1.0f - lr * weight_decay;

@@ -210,6 +210,13 @@ def adamw_step(data: np.ndarray, m: np.ndarray, v: np.ndarray, grad: np.ndarray,
                             C.c_float(beta1), C.c_float(beta2), C.c_float(eps), C.c_float(weight_decay), C.c_int(step))
 
 
+def powi(x: float, n: int) -> float:
+    """f32::powi as ops/optimizer.rs:26-27 evaluates the bias corrections."""
+    fn = lib().oracle_powi
+    fn.restype = C.c_float
+    return float(fn(C.c_float(x), C.c_int(n)))
+
+
 def _split(shape, dim):
     d = dim + len(shape) if dim < 0 else dim
     outer = int(np.prod(shape[:d], dtype=np.int64)) if d else 1

@@ -4,7 +4,7 @@ the fast TF32 mode is held to a relative Frobenius error of 2e-3."""
 import numpy as np
 import pytest
 
-from conftest import rel_fro, tol_3xtf32
+from conftest import Guarded, regression_bound_3xtf32, rel_fro, tol_3xtf32
 
 pytestmark = pytest.mark.gpu
 
@@ -34,8 +34,10 @@ def _check_fwd(F, O, a, b, *, perm_a=None, perm_b=None, bias=None, flags=0, fast
     ref = O.matmul(ha, hb)
     if bias is not None:
         ref = O.add(ref, O.HostTensor.from_array(bias))
-    out = F.matmul(da, db, _dev(F, bias) if bias is not None else None, flags=flags)
+    gout = Guarded(F, tuple(ref.shape))
+    out = F.matmul(da, db, _dev(F, bias) if bias is not None else None, flags=flags, out=gout.tensor)
     F.device_status()
+    gout.check("matmul output")
     got = out.numpy()
     assert got.shape == tuple(ref.shape)
     refn = ref.numpy()
@@ -46,6 +48,8 @@ def _check_fwd(F, O, a, b, *, perm_a=None, perm_b=None, bias=None, flags=0, fast
         bound = tol_3xtf32(k, a, b) + (1e-6 * np.max(np.abs(bias)) if bias is not None else 0)
         err = float(np.max(np.abs(got - refn))) if got.size else 0.0
         assert err <= bound, f"max err {err:.3e} > bound {bound:.3e} for {a.shape} x {b.shape}"
+        if got.size >= 256 and k >= 8:      # the regression bound: what the split really delivers
+            assert rel_fro(got, refn) <= regression_bound_3xtf32(k), (rel_fro(got, refn), a.shape, b.shape)
     return got
 
 
@@ -57,8 +61,15 @@ def _check_bwd(F, O, a, b, g, *, perm_a=None, perm_b=None, flags=0, dbias=False)
     if perm_b is not None:
         hb, db = O.permute(hb, perm_b), db.permute(perm_b)
     ra, rb = O.matmul_backward(hg, ha, hb)
-    res = F.matmul_backward(dg, da, db, flags=flags, want_dbias=dbias)
+    g_da, g_db = Guarded(F, tuple(ha.shape)), Guarded(F, tuple(hb.shape))
+    g_dbias = Guarded(F, (hb.shape[-1],)) if dbias else None
+    res = F.matmul_backward(dg, da, db, flags=flags, want_dbias=dbias, da=g_da.tensor, db=g_db.tensor,
+                            dbias=g_dbias.tensor if dbias else None)
     F.device_status()
+    g_da.check("grad_a")
+    g_db.check("grad_b")
+    if dbias:
+        g_dbias.check("dbias")
     ga, gb = res[0].numpy(), res[1].numpy()
     m, k, n = ha.shape[-2], ha.shape[-1], hb.shape[-1]
     batch_a = int(np.prod(ha.shape[:-2])) if len(ha.shape) > 2 else 1
@@ -70,6 +81,11 @@ def _check_bwd(F, O, a, b, g, *, perm_a=None, perm_b=None, flags=0, dbias=False)
     eb = float(np.max(np.abs(gb - rb.numpy())))
     assert ea <= tol_3xtf32(ka, g, b), f"dA err {ea:.3e}"
     assert eb <= tol_3xtf32(kb, a, g), f"dB err {eb:.3e}"
+    if not (flags & F._lib.PRECISION_TF32):
+        if ga.size >= 256 and ka >= 8:
+            assert rel_fro(ga, ra.numpy()) <= regression_bound_3xtf32(ka), ("dA", rel_fro(ga, ra.numpy()))
+        if gb.size >= 256 and kb >= 8:
+            assert rel_fro(gb, rb.numpy()) <= regression_bound_3xtf32(kb), ("dB", rel_fro(gb, rb.numpy()))
     if dbias:
         _, rbias = O.add_backward(hg, hg.shape, (n,))
         ebias = float(np.max(np.abs(res[2].numpy() - rbias.numpy())))

@@ -73,6 +73,28 @@ def test_clip_and_step_matches_the_cpu_backend(F, oracle, max_norm):
         assert oracle.grad_norm(rg) <= 1.0 + 1e-5        # the gradients left behind are the clipped ones
 
 
+@pytest.mark.parametrize("step", [4, 1000, 100000, 4_000_000])
+def test_adamw_bias_correction_at_large_steps(F, oracle, step):
+    """ops/optimizer.rs:26-27 use f32 powi: the library must evaluate beta^step in that order (and in O(log step)
+    host work).  At step 1000 with beta2 = 0.999 a sequential product gives a different bc2 and fails this bound."""
+    import time
+    rng = np.random.default_rng(step)
+    n = 5003
+    w = rng.standard_normal(n).astype(np.float32)
+    g = rng.standard_normal(n).astype(np.float32)
+    m = (0.1 * rng.standard_normal(n)).astype(np.float32)
+    v = np.abs(0.01 * rng.standard_normal(n)).astype(np.float32)
+    cfg = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=step)
+    dw, dm, dv, dg = (_dev(F, a) for a in (w, m, v, g))
+    t0 = time.perf_counter()
+    F.adamw_step(dw, dm, dv, dg, **cfg)
+    host_s = time.perf_counter() - t0
+    F.device_status()
+    oracle.adamw_step(w, m, v, g, **cfg)
+    assert float(np.max(np.abs(dw.numpy() - w))) <= 2e-6 * (1 + float(np.abs(w).max()))
+    assert host_s < 0.05, f"the call spent {host_s:.3f} s on the host"
+
+
 def test_adamw_rejects_step_zero(F):
     t = _dev(F, np.zeros(8, np.float32))
     with pytest.raises(Exception):

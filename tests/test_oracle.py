@@ -172,6 +172,45 @@ def test_adamw_first_step_moves_by_lr_times_sign(oracle):
     assert np.allclose(m, 0.09 * g, rtol=1e-6)
 
 
+def _powi_f32(x, n):
+    """Independent restatement of f32::powi (binary exponentiation, lowest bit first) in numpy float32."""
+    x, r = np.float32(x), np.float32(1.0)
+    while True:
+        if n & 1:
+            r = np.float32(r * x)
+        n >>= 1
+        if n == 0:
+            return float(r)
+        x = np.float32(x * x)
+
+
+def test_bias_correction_uses_powi_rounding(oracle):
+    """ops/optimizer.rs:26-27: bc = 1 - beta.powi(step).  powi squares repeatedly, so from step 4 on it rounds
+    differently from `step` successive multiplications; large steps must follow powi, in O(log step)."""
+    for beta in (0.9, 0.95, 0.999):
+        for step in (1, 2, 3, 4, 7, 1000, 100000):
+            assert oracle.powi(beta, step) == _powi_f32(beta, step), (beta, step)
+    # hand-derived: 0.5^10 is exact, 2^-20 too; a negative exponent takes the reciprocal
+    assert oracle.powi(0.5, 10) == 2.0 ** -10 and oracle.powi(2.0, -20) == 2.0 ** -20
+    # the two evaluation orders do differ in f32 (this is what the parity case at step 1000 guards)
+    seq = np.float32(1.0)
+    for _ in range(1000):
+        seq = np.float32(seq * np.float32(0.999))
+    assert float(seq) != oracle.powi(0.999, 1000)
+    # and the step itself follows: one AdamW step at step = 1000 against the formula in float64 with powi's bc
+    rng = np.random.default_rng(5)
+    w, g = rng.standard_normal(257).astype(np.float32), rng.standard_normal(257).astype(np.float32)
+    m, v = (0.1 * rng.standard_normal(257)).astype(np.float32), np.abs(0.01 * rng.standard_normal(257)).astype(np.float32)
+    w0, m0, v0 = w.copy(), m.copy(), v.copy()
+    oracle.adamw_step(w, m, v, g, lr=1e-3, beta1=0.9, beta2=0.999, step=1000)
+    bc1 = 1.0 - _powi_f32(0.9, 1000)
+    bc2 = np.float32(1.0) - np.float32(_powi_f32(0.999, 1000))
+    m1 = np.float32(0.9) * m0 + (np.float32(1.0) - np.float32(0.9)) * g
+    v1 = np.float32(0.999) * v0 + (np.float32(1.0) - np.float32(0.999)) * g * g
+    want = w0.astype(np.float64) - 1e-3 * (m1.astype(np.float64) / bc1) / (np.sqrt(v1.astype(np.float64) / float(bc2)) + 1e-8)
+    assert np.max(np.abs(w - want)) < 2e-6
+
+
 def test_clip_and_step_scales_the_gradients_in_place(oracle):
     """ops/optimizer.rs:226-245: the norm is returned unclipped, the gradients are left scaled to max_grad_norm."""
     g = [np.full(4, 3.0, np.float32), np.full(9, 4.0, np.float32)]       # norm = sqrt(36 + 144)

@@ -64,6 +64,39 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row(F):
     assert float(np.max(np.abs(got_db - ref_db))) <= 1e-5 * 50 * float(np.abs(dy).max())
 
 
+def test_device_memory_does_not_move_and_results_are_bitwise_equal(F):
+    """What the entry point is for: after the library's own scratch has been released, so that the regular
+    entry point would have to cudaMalloc, a call through the allocation-free one leaves the device's free
+    memory exactly where it was.  The outputs are bitwise those of the regular entry point (same kernels,
+    same summation order), also when a call on other data ran in between and left its partial sums in the
+    shared array."""
+    import torch
+    from framework_b200.tensor import current_stream
+    lib = F._lib.lib()
+    rng = np.random.default_rng(33)
+    rows, n = 6000, 1536
+    dy_np = rng.standard_normal((rows, n), dtype=np.float32)
+    other_np = rng.standard_normal((900, 2048), dtype=np.float32)
+    dy, other = F.DeviceTensor.from_numpy(dy_np), F.DeviceTensor.from_numpy(other_np)
+    outs = {k: torch.full((n,), float("nan"), device="cuda") for k in ("first", "again", "regular")}
+    other_out = torch.empty(2048, device="cuda")
+    torch.cuda.synchronize()
+    F._lib.check(lib.mni_b200_release())                 # drop the growable scratch: a regular call must allocate now
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    F._lib.check(lib.mni_b200_add_bias_bwd_noalloc(dy.ptr, None, outs["first"].data_ptr(), rows, n, 0, current_stream()))
+    F._lib.check(lib.mni_b200_add_bias_bwd_noalloc(other.ptr, None, other_out.data_ptr(), 900, 2048, 0, current_stream()))
+    F._lib.check(lib.mni_b200_add_bias_bwd_noalloc(dy.ptr, None, outs["again"].data_ptr(), rows, n, 0, current_stream()))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, "device memory moved during allocation-free calls"
+    F._lib.check(lib.mni_b200_add_bias_bwd(dy.ptr, None, outs["regular"].data_ptr(), rows, n, 0, current_stream()))
+    torch.cuda.synchronize()
+    first, again, regular = (outs[k].cpu().numpy() for k in ("first", "again", "regular"))
+    assert np.array_equal(first, regular) and np.array_equal(again, regular)
+    assert float(np.max(np.abs(regular - dy_np.astype(np.float64).sum(0)))) <= 1e-5 * rows * float(np.abs(dy_np).max())
+    assert float(np.max(np.abs(other_out.cpu().numpy() - other_np.astype(np.float64).sum(0)))) <= 1e-5 * 900 * 6.0
+
+
 def test_refuses_sizes_beyond_the_built_in_scratch(F):
     import torch
     from framework_b200.tensor import current_stream
