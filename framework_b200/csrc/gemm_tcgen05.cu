@@ -86,6 +86,7 @@ struct KParams {
     int kiters;                // k-blocks per folded batch
     int fold;
     int splits;
+    int chunk_iters;           // longest run of k-blocks summed in one tensor-memory accumulator (0 = no limit)
     int a_batch, a_d1, a_d2;   // operand flat batch count and inner dim sizes
     int b_batch, b_d1, b_d2;
     int a_mode, b_mode;        // OperandMode
@@ -333,6 +334,7 @@ struct TileCoord {
     int shared;      // balanced tail: this unit is only a range of the tile's k-blocks
     int park;        // shared: which of the CTA's two parking places it uses (0 = first unit of its range)
     int tile;        // flat tile index
+    int chunk;       // > 0: a later piece of a unit whose contraction is summed in several accumulators (added to the output)
 };
 
 __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit) {
@@ -341,6 +343,7 @@ __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit) {
     t.split = unit - tile * p.splits;
     t.shared = 0;
     t.park = 0;
+    t.chunk = 0;
     t.tile = tile;
     const int per_batch = p.tiles_m * p.tiles_n;
     t.bt = fd_div(tile, p.fd_per_batch);
@@ -369,6 +372,11 @@ __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit) {
 struct WorkIter {
     int unit, unit_step, unit_end;     // whole units
     long long w0, w, w1;               // tail range in k-blocks, relative to the tail's first tile
+    // A unit with a long contraction is handed out as consecutive pieces of at most p.chunk_iters k-blocks:
+    // the tensor core's f32 accumulate truncates, so one long chain loses ~7e-9 * K of relative accuracy;
+    // every piece gets a fresh accumulator and the epilogue adds it to the output (round-to-nearest adds).
+    TileCoord cur;                     // the unit being handed out in pieces
+    int piece_it, piece_end, piece_len, piece_no;
 };
 __device__ __forceinline__ long long sk_range_begin(const KParams &p, int slot, int nslots) {
     const long long total = static_cast<long long>(p.batch * p.tiles_m * p.tiles_n - p.sk_first_tile) * (p.fold * p.kiters);
@@ -380,6 +388,7 @@ __device__ __forceinline__ WorkIter work_begin(const KParams &p, int slot, int n
     wi.unit_step = nslots;
     wi.unit_end = p.sk ? p.sk_first_tile : p.batch * p.tiles_m * p.tiles_n * p.splits;
     wi.w0 = wi.w = wi.w1 = 0;
+    wi.piece_it = wi.piece_end = wi.piece_len = wi.piece_no = 0;
     if (p.sk) {
         wi.w0 = wi.w = sk_range_begin(p, slot, nslots);
         wi.w1 = sk_range_begin(p, slot + 1, nslots);
@@ -388,9 +397,27 @@ __device__ __forceinline__ WorkIter work_begin(const KParams &p, int slot, int n
 }
 __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit);
 __device__ __forceinline__ bool work_next(const KParams &p, WorkIter &wi, TileCoord &t) {
+    if (wi.piece_it < wi.piece_end) {          // next piece of the current unit
+        t = wi.cur;
+        t.it0 = wi.piece_it;
+        t.it1 = min(wi.piece_end, wi.piece_it + wi.piece_len);
+        t.chunk = ++wi.piece_no;
+        wi.piece_it = t.it1;
+        return true;
+    }
     if (wi.unit < wi.unit_end) {
         t = decode_unit(p, wi.unit);
         wi.unit += wi.unit_step;
+        const int len = t.it1 - t.it0;
+        if (p.chunk_iters > 0 && len > p.chunk_iters + (p.chunk_iters >> 1)) {
+            const int pieces = (len + p.chunk_iters - 1) / p.chunk_iters;
+            wi.cur = t;
+            wi.piece_len = (len + pieces - 1) / pieces;      // equal pieces
+            wi.piece_end = t.it1;
+            wi.piece_no = 0;
+            t.it1 = t.it0 + wi.piece_len;
+            wi.piece_it = t.it1;
+        }
         return true;
     }
     if (wi.w < wi.w1) {
@@ -540,7 +567,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             TileCoord t;
             while (ok && work_next(p, wi, t)) {
                 int f = 0, kk = t.it0;
-                if (p.fold > 1 || p.splits > 1 || p.sk) {
+                if (t.it0 >= p.kiters) {
                     f = t.it0 / p.kiters;
                     kk = t.it0 - f * p.kiters;
                 }
@@ -796,6 +823,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (!ok) break;
             tc_fence_after();
             const bool fuse = p.splits == 1;
+            const bool add_piece = t.chunk > 0;       // a later piece of this unit's contraction: added to what the earlier ones wrote
+            if (add_piece && use_tma) {
+                // this warp's earlier stores to the same patches must have completed, not just been read
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                in_flight = 0;
+                __syncwarp();
+            }
             const int row0 = t.tm * (BM * CG) + static_cast<int>(cta_rank) * BM + q * 32;
             const int cbatch = fuse ? t.bt : t.split * p.batch + t.bt;
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
@@ -970,7 +1004,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     };
                     const bool do_act = fuse && p.act != 0;          // host guarantees use_tma in this mode
                     if (do_act && p.store_pre) emit(&tmC, false);    // the raw product, what the tape saves
-                    if (fuse && p.bias != nullptr && p.transpose_out) {
+                    if (fuse && p.bias != nullptr && add_piece) {
+                        // the bias went in with the first piece
+                    } else if (fuse && p.bias != nullptr && p.transpose_out) {
                         const float b = row0 + lane < p.M ? __ldg(p.bias + row0 + lane) : 0.f;   // one bias value per row here
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
@@ -995,7 +1031,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(gelu_tanh_f(__uint_as_float(v[j])));
                         emit(&tmD, false);
                     } else if (use_tma) {
-                        emit(&tmC, p.epi_mode == kEpiTmaReduce && fuse);
+                        emit(&tmC, (p.epi_mode == kEpiTmaReduce && fuse) || add_piece);
                     } else {
                         const int row = row0 + lane;
                         if (row < p.M) {
@@ -1009,7 +1045,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                     float y[8];
 #pragma unroll
                                     for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(v[8 * j + e]);
-                                    if (fuse && p.accumulate) {
+                                    if ((fuse && p.accumulate) || add_piece) {
                                         float o[8];
                                         asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                                                      : "=f"(o[0]), "=f"(o[1]), "=f"(o[2]), "=f"(o[3]), "=f"(o[4]), "=f"(o[5]),
@@ -1029,7 +1065,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             for (int j = 0; j < 32; ++j) {
                                 if (col0 + j < p.N) {
                                     float y = __uint_as_float(v[j]);
-                                    if (fuse && p.accumulate) y += out[col0 + j];
+                                    if ((fuse && p.accumulate) || add_piece) y += out[col0 + j];
                                     out[col0 + j] = y;
                                 }
                             }
@@ -1337,11 +1373,14 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
         for (int bn : {256, 128, 64}) {
             if (bn > 64 && p.N <= bn / 2) continue;               // no tile wider than the output needs
             const int cg = pair_for(bn);
-            const double c_ns = bn == 256 ? (cg == 2 ? 30.0 : 33.0) : (bn == 128 ? 15.4 : 13.5);
             const long long tiles = static_cast<long long>(p.batch) * ((p.M + BM * cg - 1) / (BM * cg)) * ((p.N + bn - 1) / bn);
             const long long slots = std::max(1, sm_count / cg);
             for (int sp : {1, 2, 3, 4, 6, 8, 12, 16}) {
                 if (sp > 1 && (tiles * sp > slots || k_eff / sp < 64.0)) continue;
+                // A 128-wide tile with a long contraction runs at its steady state, which shared-memory bandwidth
+                // sets (128 KB per 32-deep k-block = 1000 cycles): measured 20.5 ns per k element at K = 8192,
+                // against 32 for a 256-wide pair doing twice the work.
+                const double c_ns = bn == 256 ? (cg == 2 ? 30.0 : 33.0) : (bn == 128 ? (k_eff / sp >= 1024.0 ? 20.5 : 15.4) : 13.5);
                 const double rounds = static_cast<double>((tiles * sp + slots - 1) / slots);
                 const double t = rounds * (k_eff / sp) * c_ns + (sp > 1 ? 1500.0 + (sp + 1) * out_bytes / 3000.0 : 0.0);
                 if (t < best) { best = t; pl.bn = bn; model_splits = sp; }
@@ -1597,6 +1636,12 @@ int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, in
     k.kiters = static_cast<int>((p.K + pl.bk - 1) / pl.bk);
     k.fold = static_cast<int>(p.fold);
     k.splits = pl.splits;
+    {
+        // Longest accumulation chain in tensor memory, in contraction elements (MNI_B200_CHUNK_K, 0 = unlimited).
+        // The fused activation needs the whole sum in one accumulator.
+        const int chunk_k = env_int("MNI_B200_CHUNK_K", 1024);
+        k.chunk_iters = (chunk_k > 0 && p.D == nullptr) ? std::max(1, chunk_k / pl.bk) : 0;
+    }
     k.a_batch = static_cast<int>(p.A.batch);
     k.a_d1 = static_cast<int>(p.A.bshape[1]);
     k.a_d2 = static_cast<int>(p.A.bshape[2]);

@@ -1,1 +1,1 @@
-__attribute__((visibility("default"))) const char *mni_b200_build_id(void) { return "2e9c919172fa2f00b2649c323e60c9bd71f73ec5b81431f96505819270f2f8d8"; }
+__attribute__((visibility("default"))) const char *mni_b200_build_id(void) { return "29d421111da130e27cca23639209781e1e095b066441c9ff9c1802a2c09eee0b"; }
