@@ -71,6 +71,7 @@ _SIGNATURES = {
                                       C.c_float, C.c_float, C.c_float, C.c_uint32, C.c_void_p, C.c_float, C.c_int,
                                       C.c_void_p]),
     "mni_b200_contiguous": (C.c_int, [C.POINTER(View), C.c_void_p, C.c_void_p]),
+    "mni_b200_sm_reserve": (C.c_int, [C.c_int]),
     "mni_b200_workspace_set": (C.c_int, [C.c_void_p, C.c_size_t]),
     "mni_b200_workspace_query": (C.c_int, [C.POINTER(View), C.POINTER(View), C.c_uint32, C.POINTER(C.c_size_t)]),
     "mni_b200_device_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),

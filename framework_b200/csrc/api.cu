@@ -28,6 +28,7 @@ struct DeviceState {
     std::mutex mu;
     bool init = false;
     int sm_count = 0;
+    int sm_reserve = 0;           // SMs the tensor-core launches leave free (mni_b200_sm_reserve)
     int cc_major = 0;
     uint8_t *ws = nullptr;        // library-owned scratch
     size_t ws_bytes = 0;
@@ -242,7 +243,10 @@ struct Call {
     cudaStream_t stream;
     uint32_t flags;
     uint8_t *base = nullptr;   // resolved scratch base (real mode, second pass)
-    int flag_bank = 0;         // 1 while launches go to the library's side stream
+    int flag_bank = 0;         // 1 while launches go to the library's side stream / for the second product of a pair
+    int dep_mode = 0;          // GemmProblem::dep_mode of the tensor-path launches issued now
+    // SMs the persistent tensor-core grids are planned for: all of them minus the caller's reservation
+    int gemm_sms() const { return std::max(8, st->sm_count - st->sm_reserve); }
     bool dry() const { return arena.dry; }
     float *at(size_t off) const { return reinterpret_cast<float *>(base + off); }
 };
@@ -281,15 +285,16 @@ int run_gemm(Call &c, GemmProblem &p) {
     p.fast_tf32 = (c.flags & MNI_B200_PRECISION_TF32) != 0;
     p.force_splits = static_cast<int>((c.flags >> 16) & 0xffu);
     p.flag_bank = c.flag_bank;
+    p.dep_mode = c.dep_mode;
     if (p.M > 0x7fffffffLL || p.N > 0x7fffffffLL || p.K > 0x7fffffffLL || p.batch * p.fold > 0x7fffffffLL ||
         p.batch * ((p.M + 127) / 128) * ((p.N + 63) / 64) > 0x3fffffffLL)
         return fail(MNI_B200_ERR_TOO_LARGE, "GEMM %lld x %lld x %lld (batch %lld) exceeds the kernels' int32 indexing",
                     (long long)p.M, (long long)p.N, (long long)p.K, (long long)p.batch);
-    const size_t pbytes = gemm_tc_partial_bytes(p, c.st->sm_count);
+    const size_t pbytes = gemm_tc_partial_bytes(p, c.gemm_sms());
     size_t poff = 0;
     if (pbytes) poff = c.arena.reserve(pbytes);
     if (c.dry()) return MNI_B200_OK;
-    return launch_gemm_tc(p, pbytes ? c.at(poff) : nullptr, c.st->err_word, c.st->sm_count, c.stream);
+    return launch_gemm_tc(p, pbytes ? c.at(poff) : nullptr, c.st->err_word, c.gemm_sms(), c.stream);
 }
 
 int zero_or_bias_fill(Call &c, float *out, int64_t rows, int64_t n, const float *bias, bool accumulate) {
@@ -398,7 +403,7 @@ int fwd_gelu_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const
         p.bias = bias;
         p.fast_tf32 = (c.flags & MNI_B200_PRECISION_TF32) != 0;
         p.force_splits = static_cast<int>((c.flags >> 16) & 0xffu);
-        if (gemm_tc_can_fuse_activation(p, c.st->sm_count)) {
+        if (gemm_tc_can_fuse_activation(p, c.gemm_sms())) {
             rc = run_gemm(c, p);
             c.flags = saved_flags;
             return rc;
@@ -477,14 +482,35 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
     const bool acc_dbias = (c.flags & MNI_B200_ACCUMULATE_DBIAS) != 0;
     const int64_t a_elems = s.a_batch * s.M * s.K, b_elems = s.b_batch * s.K * s.N;
 
-    // The two gradient products of a small problem each fill only part of the GPU, a skinny one's are short,
-    // launch-bound kernels, and a medium one's leave a ragged last wave: issue grad_b on the side stream next
-    // to grad_a and join before returning.  The column sums of the bias gradient are HBM-bound and always go
-    // to the side stream, where they run beside the tensor-bound products instead of in front of them.
+    // Which kernel each gradient takes.
+    const bool da_wanted = da && a_elems > 0 && s.N > 0 && g_batch > 0;
+    const bool db_wanted = db && b_elems > 0 && s.M > 0 && g_batch > 0;
+    const bool skinny_dx = da_wanted &&
+                           ((c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
+                            ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= kSkinnyDxRows)) &&
+                           s.batch == 1 && g_batch == 1 && s.a_batch == 1 && s.b_batch == 1 &&
+                           dc->stride[gn - 1] == 1 && b->stride[b->ndim - 1] == 1 && s.K > 1 &&
+                           skinny_dx_supported(dc->ptr, dc->stride[gn - 2], b->ptr, b->stride[b->ndim - 2], s.M, s.N);
+    const bool skinny_dw = db_wanted &&
+                           ((c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
+                            ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= kSkinnyDwRows)) &&
+                           s.batch == 1 && g_batch == 1 && s.M <= 16 && (a->stride[a->ndim - 1] == 1 || s.K == 1) &&
+                           (dc->stride[gn - 1] == 1 || s.N == 1);
+
+    // grad_a and grad_b do not depend on each other.  grad_b of a small problem goes to the library's side stream
+    // next to grad_a and is joined before returning (event fork / join, also valid under stream capture).  The
+    // column sums of the bias gradient are HBM-bound and always go to the side stream, where they run beside the
+    // tensor-bound products instead of in front of them.
+    // MNI_B200_BWD_PAIR=1 selects the one-stream alternative for two tensor-core products: launched back to back
+    // as an independent pair (GemmProblem::dep_mode), the second starts on the SMs the first leaves free with no
+    // event in between.  Measured, it does not pay: 512^3 30.9 vs 28.8 us per step under graph replay (the second
+    // product can only start once every CTA of the first has passed its own dependency wait), 58.9 vs 60.8 us
+    // eager, the Linear step 406 vs 405 us -- so it stays off.
     const double work = static_cast<double>(s.M) * static_cast<double>(s.N) * static_cast<double>(s.K) *
                         static_cast<double>(std::max<int64_t>(g_batch, 1));
     const bool side_on = !c.dry() && env_flag("MNI_B200_BWD_OVERLAP", 1);
-    const bool overlap = side_on && da && db && a_elems > 0 && b_elems > 0 && work > 0 && work <= overlap_work_limit();
+    const bool pair = side_on && da_wanted && db_wanted && !skinny_dx && !skinny_dw && env_flag("MNI_B200_BWD_PAIR", 0);
+    const bool overlap = side_on && !pair && da && db && a_elems > 0 && b_elems > 0 && work > 0 && work <= overlap_work_limit();
     const bool side_dbias = side_on && dbias && (da || db) && work > 0;
     cudaStream_t const main_stream = c.stream;
     if (overlap || side_dbias) {
@@ -495,6 +521,7 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
         Call &c; cudaStream_t main; bool on;
         ~Join() {
             c.flag_bank = 0;
+            c.dep_mode = 0;
             if (!on) return;
             c.stream = main;
             if (cudaEventRecord(c.st->ev_join, c.st->side) == cudaSuccess) cudaStreamWaitEvent(main, c.st->ev_join, 0);
@@ -540,22 +567,16 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
 
     // grad_a = unbroadcast(dc . b^T, a.shape)   (ops/matmul.rs:231-240)
     if (da && a_elems > 0) {
-        if (s.N == 0 || g_batch == 0) {
+        if (!da_wanted) {
             rc = zero_or_bias_fill(c, da, a_elems, 1, nullptr, acc_da);
             if (rc) return rc;
+        } else if (skinny_dx) {
+            if (!c.dry()) {
+                rc = launch_skinny_dx(dc->ptr, dc->stride[gn - 2], b->ptr, b->stride[b->ndim - 2], da, s.K, acc_da,
+                                      s.M, s.N, s.K, c.stream);
+                if (rc) return rc;
+            }
         } else {
-            const bool skinny_dx = ((c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
-                                    ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= kSkinnyDxRows)) &&
-                                   s.batch == 1 && g_batch == 1 && s.a_batch == 1 && s.b_batch == 1 &&
-                                   dc->stride[gn - 1] == 1 && b->stride[b->ndim - 1] == 1 && s.K > 1 &&
-                                   skinny_dx_supported(dc->ptr, dc->stride[gn - 2], b->ptr, b->stride[b->ndim - 2], s.M, s.N);
-            if (skinny_dx) {
-                if (!c.dry()) {
-                    rc = launch_skinny_dx(dc->ptr, dc->stride[gn - 2], b->ptr, b->stride[b->ndim - 2], da, s.K, acc_da,
-                                          s.M, s.N, s.K, c.stream);
-                    if (rc) return rc;
-                }
-            } else {
             int64_t ob[MNI_B200_MAX_DIMS];
             const int onb = broadcast_shape(dc->shape, gn - 2, b->shape, b->ndim - 2, ob);
             if (onb < 0) return fail(MNI_B200_ERR_BROADCAST, "dc and b batch shapes are not broadcastable");
@@ -566,43 +587,43 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
             if (rc) return rc;
             X.batch = g_batch;
             Y.batch = s.b_batch;
+            c.dep_mode = pair ? 1 : 0;
             rc = grad_gemm(c, X, Y, s.M, s.K, s.N, ob, onb, *a, da, acc_da);
+            c.dep_mode = 0;
             if (rc) return rc;
-            }
         }
     }
 
     // grad_b = unbroadcast(a^T . dc, b.shape)   (ops/matmul.rs:242-251)
     if (overlap) { c.stream = c.st->side; c.flag_bank = 1; }
     if (db && b_elems > 0) {
-        if (s.M == 0 || g_batch == 0) {
+        if (!db_wanted) {
             rc = zero_or_bias_fill(c, db, b_elems, 1, nullptr, acc_db);
             if (rc) return rc;
-        } else {
-            const bool want_skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
-                                     ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= kSkinnyDwRows);
-            const bool plain2d = s.batch == 1 && g_batch == 1 && s.M <= 16;
-            if (want_skinny && plain2d && (a->stride[a->ndim - 1] == 1 || s.K == 1) &&
-                (dc->stride[gn - 1] == 1 || s.N == 1)) {
-                if (!c.dry()) {
-                    rc = launch_skinny_dw(a->ptr, a->stride[a->ndim - 2], dc->ptr, dc->stride[gn - 2], db, s.N, acc_db,
-                                          s.M, s.N, s.K, c.stream);
-                    if (rc) return rc;
-                }
-            } else {
-                int64_t ob[MNI_B200_MAX_DIMS];
-                const int onb = broadcast_shape(a->shape, a->ndim - 2, dc->shape, gn - 2, ob);
-                if (onb < 0) return fail(MNI_B200_ERR_BROADCAST, "a and dc batch shapes are not broadcastable");
-                Operand X, Y;
-                rc = make_operand(c, *a, true, X);     // rows K, contraction M
-                if (rc) return rc;
-                rc = make_operand(c, *dc, true, Y);    // rows N, contraction M
-                if (rc) return rc;
-                X.batch = s.a_batch;
-                Y.batch = g_batch;
-                rc = grad_gemm(c, X, Y, s.K, s.N, s.M, ob, onb, *b, db, acc_db);
+        } else if (skinny_dw) {
+            if (!c.dry()) {
+                rc = launch_skinny_dw(a->ptr, a->stride[a->ndim - 2], dc->ptr, dc->stride[gn - 2], db, s.N, acc_db,
+                                      s.M, s.N, s.K, c.stream);
                 if (rc) return rc;
             }
+        } else {
+            int64_t ob[MNI_B200_MAX_DIMS];
+            const int onb = broadcast_shape(a->shape, a->ndim - 2, dc->shape, gn - 2, ob);
+            if (onb < 0) return fail(MNI_B200_ERR_BROADCAST, "a and dc batch shapes are not broadcastable");
+            Operand X, Y;
+            const size_t used_before = c.arena.used;
+            rc = make_operand(c, *a, true, X);     // rows K, contraction M
+            if (rc) return rc;
+            rc = make_operand(c, *dc, true, Y);    // rows N, contraction M
+            if (rc) return rc;
+            X.batch = s.a_batch;
+            Y.batch = g_batch;
+            // An operand that had to be gathered first makes this product depend on the gather kernel just
+            // launched: then it waits like any other launch.
+            if (pair && c.arena.used == used_before) { c.dep_mode = 2; c.flag_bank = 1; }
+            rc = grad_gemm(c, X, Y, s.K, s.N, s.M, ob, onb, *b, db, acc_db);
+            c.dep_mode = 0;
+            if (rc) return rc;
         }
     }
     return MNI_B200_OK;
@@ -815,6 +836,16 @@ int mni_b200_contiguous(const mni_b200_view *src, float *dst, void *stream) {
     rc = device_state(&st);
     if (rc) return rc;
     return launch_pack(*src, dst, src->shape[src->ndim - 1], static_cast<cudaStream_t>(stream));
+}
+
+int mni_b200_sm_reserve(int sms) {
+    if (sms < 0) return fail(MNI_B200_ERR_ARG, "negative SM count");
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(st->mu);
+    st->sm_reserve = std::min(sms, std::max(0, st->sm_count - 8));
+    return MNI_B200_OK;
 }
 
 int mni_b200_workspace_set(void *ptr, size_t bytes) {

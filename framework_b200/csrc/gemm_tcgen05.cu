@@ -86,6 +86,7 @@ struct KParams {
     int kiters;                // k-blocks per folded batch
     int fold;
     int splits;
+    int dep_mode;              // 0: depends on everything before it; 1 / 2: first / second of two independent products (see GemmProblem)
     int chunk_iters;           // longest run of k-blocks summed in one tensor-memory accumulator (0 = no limit)
     int a_batch, a_d1, a_d2;   // operand flat batch count and inner dim sizes
     int b_batch, b_d1, b_d2;
@@ -507,7 +508,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int unit0 = static_cast<int>(blockIdx.x) / CG;           // this CTA (pair) starts at this unit ...
     const int unit_step = static_cast<int>(gridDim.x) / CG;        // ... and strides by the number of CTAs (pairs)
 
-    if (threadIdx.x == 0) grid_dependency_trigger();    // the next grid in the stream may be scheduled already
+    // The next grid in the stream may be scheduled already -- unless it is the independent second product of
+    // a pair, which skips its own wait: then it may only start once this grid's predecessors are known complete.
+    if (threadIdx.x == 0 && p.dep_mode != 1) grid_dependency_trigger();
     if (warp == 0 && lane == 1) {
         // descriptor fetches overlap the barrier and TMEM set-up
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
@@ -548,7 +551,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if constexpr (CG == 2) cluster_sync_all();   // the peer's barriers exist before anyone arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    grid_dependency_wait();      // everything above overlapped the previous grid; its results are needed from here on
+    // Everything above overlapped the previous grid; its results are needed from here on.  The second product of
+    // an independent pair needs nothing from the first: it runs beside it and waits for it only before it ends.
+    if (p.dep_mode != 2) grid_dependency_wait();
+    if (p.dep_mode == 1 && threadIdx.x == 0) grid_dependency_trigger();
 
 
     if (warp == 0) {
@@ -1126,6 +1132,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
                          : "memory");
     }
+    // Stream order for whatever follows: this grid may not complete before the grid it ran beside has.
+    if (p.dep_mode == 2 && threadIdx.x == 0) grid_dependency_wait();
 }
 
 // Deterministic split-K finish: C = sum_s partial[s] (+ bias) (+ C), splits added in ascending order.
@@ -1636,6 +1644,7 @@ int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, in
     k.kiters = static_cast<int>((p.K + pl.bk - 1) / pl.bk);
     k.fold = static_cast<int>(p.fold);
     k.splits = pl.splits;
+    k.dep_mode = p.dep_mode;
     {
         // Longest accumulation chain in tensor memory, in contraction elements (MNI_B200_CHUNK_K, 0 = unlimited).
         // The fused activation needs the whole sum in one accumulator.

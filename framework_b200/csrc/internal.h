@@ -95,6 +95,11 @@ struct GemmProblem {
     bool accumulate = false;       // C += ...
     bool fast_tf32 = false;        // one TF32 pass instead of the 3-pass split
     int force_splits = 0;          // tests
+    // Two products of one call that do not depend on each other (grad_a and grad_b) are launched back to back on
+    // one stream as a pair: the first (1) lets its dependent start only after its own wait for earlier work has
+    // returned, the second (2) skips that wait, runs beside the first -- on free SMs, or on the SMs its tail
+    // leaves -- and waits for it just before it ends, so stream order holds for everything after the pair.
+    int dep_mode = 0;
     int flag_bank = 0;             // 1 for launches on the library's side stream: their own set of balanced-tail flags
     // Optional second output D = gelu(C + bias) written by the same epilogue (C itself is skipped if null).
     float *D = nullptr;

@@ -509,6 +509,106 @@ skinny_dx_kernel(const float *__restrict__ dy, long long lddy, const float *__re
     }
 }
 
+// Second form of dx = dy . W^T, used from 3 rows up.  In the kernel above a warp walks its two weight rows
+// through all of N: eight sequential steps, each a full DRAM round trip, and 4 * MT loads of dy (from L1) per
+// step.  Here a block of 8 warps owns 16 weight rows and each warp owns a 128 * P-float slice of N for all 16
+// rows: its dy slice is loaded ONCE into registers (MT * P 16-byte vectors) and stays there while the warp
+// streams the 16 rows' slice in row pairs, the next pair's weight loads issued before the current pair is
+// multiplied, so two pairs (4 * P 16-byte loads per lane) are always in flight.  Lane sums are folded with
+// shuffles, a warp adds its slices into its own line of shared memory, and after one block barrier the
+// block's first threads add the 8 warps' lines in warp order (fixed order: bit-reproducible) and write dx.
+constexpr int kDxsWarps = 8;
+constexpr int kDxsRows = 16;
+template <int MT, int P, int MINB>
+__global__ void __launch_bounds__(32 * kDxsWarps, MINB)
+skinny_dx_sliced_kernel(const float *__restrict__ dy, long long lddy, const float *__restrict__ W, long long ldw,
+                        float *__restrict__ dx, long long lddx, int accumulate, int M, long long N, long long K) {
+    __shared__ float part[kDxsWarps][kDxsRows][MT];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long k0 = static_cast<long long>(blockIdx.x) * kDxsRows;
+    for (int i = lane; i < kDxsRows * MT; i += 32) (&part[warp][0][0])[i] = 0.f;
+    __syncwarp();
+    const long long slice_w = 128LL * P;
+    const long long nslices = (N + slice_w - 1) / slice_w;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (long long slice = warp; slice < nslices; slice += kDxsWarps) {
+        const long long n0 = slice * slice_w + lane * 4;
+        float4 g[MT][P];
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int q = 0; q < P; ++q) {
+                const long long nq = n0 + 128 * q;
+                g[m][q] = (m < M && nq < N) ? __ldg(reinterpret_cast<const float4 *>(dy + m * lddy + nq)) : zero4;
+            }
+        auto load_pair = [&](int pr, float4 (&wa)[P], float4 (&wb)[P]) {
+            // rows past K repeat the last row: loaded, never stored
+            const long long ra = min(k0 + 2 * pr, K - 1), rb = min(k0 + 2 * pr + 1, K - 1);
+            const float *pa = W + ra * ldw, *pb = W + rb * ldw;
+#pragma unroll
+            for (int q = 0; q < P; ++q) {
+                const long long nq = n0 + 128 * q;
+                if (nq < N) {
+                    wa[q] = __ldcs(reinterpret_cast<const float4 *>(pa + nq));
+                    wb[q] = __ldcs(reinterpret_cast<const float4 *>(pb + nq));
+                } else {
+                    wa[q] = zero4;
+                    wb[q] = zero4;
+                }
+            }
+        };
+        float4 wa[P], wb[P], na[P], nb[P];
+        load_pair(0, wa, wb);
+#pragma unroll
+        for (int pr = 0; pr < kDxsRows / 2; ++pr) {
+            if (pr + 1 < kDxsRows / 2) load_pair(pr + 1, na, nb);
+            float acc[2][MT];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                acc[0][m] = 0.f;
+                acc[1][m] = 0.f;
+#pragma unroll
+                for (int q = 0; q < P; ++q) {
+                    const float4 gv = g[m][q];
+                    acc[0][m] = fmaf(gv.x, wa[q].x, fmaf(gv.y, wa[q].y, fmaf(gv.z, wa[q].z, fmaf(gv.w, wa[q].w, acc[0][m]))));
+                    acc[1][m] = fmaf(gv.x, wb[q].x, fmaf(gv.y, wb[q].y, fmaf(gv.z, wb[q].z, fmaf(gv.w, wb[q].w, acc[1][m]))));
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    float v = acc[r][m];
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                    if (lane == 0) part[warp][2 * pr + r][m] += v;
+                }
+            if (pr + 1 < kDxsRows / 2) {
+#pragma unroll
+                for (int q = 0; q < P; ++q) { wa[q] = na[q]; wb[q] = nb[q]; }
+            }
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kDxsRows * MT; i += 32 * kDxsWarps) {
+        const int row = i / MT, m = i - row * MT;
+        if (m >= M || k0 + row >= K) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDxsWarps; ++w) v += part[w][row][m];
+        float *dst = dx + m * lddx + k0 + row;
+        *dst = accumulate ? *dst + v : v;
+    }
+}
+
+// Which dx kernel runs.  The sliced kernel is opt-in (MNI_B200_SKINNY_DX_SLICED=1): measured inside the
+// benchmark step at 4 rows, K = N = 4096, it needs ~28 us against ~18 us for the row-pair kernel.
+int dx_sliced_mode() {
+    const char *v = getenv("MNI_B200_SKINNY_DX_SLICED");
+    return v && *v ? atoi(v) : -1;
+}
+
 int pick_mt(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16; }
 
 struct FwdPlan { int splits; long long k_per; int strips; bool ring; bool cluster = false; };
@@ -661,6 +761,33 @@ bool skinny_dx_supported(const float *dy, int64_t lddy, const float *W, int64_t 
 int launch_skinny_dx(const float *dy, int64_t lddy, const float *W, int64_t ldw, float *dx, int64_t lddx,
                      bool accumulate, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
     const int mt = pick_mt(M);
+    const int sliced = dx_sliced_mode();
+    if (sliced > 0) {
+        const unsigned sblocks = static_cast<unsigned>((K + kDxsRows - 1) / kDxsRows);
+#define MNI_SKINNY_DXS(MT, P_, B_)                                                                              \
+    skinny_dx_sliced_kernel<MT, P_, B_><<<sblocks, 32 * kDxsWarps, 0, stream>>>(dy, lddy, W, ldw, dx, lddx,       \
+                                                                               accumulate ? 1 : 0, (int)M, N, K)
+        const char *vv = getenv("MNI_B200_DXS_VARIANT");      // register / slice-width variants of the 4- and 8-row forms
+        const int variant = vv && *vv ? atoi(vv) : 0;
+        switch (mt) {
+            case 1: MNI_SKINNY_DXS(1, 4, 2); break;
+            case 2: MNI_SKINNY_DXS(2, 4, 2); break;
+            case 4:
+                if (variant == 1) MNI_SKINNY_DXS(4, 4, 1);
+                else if (variant == 2) MNI_SKINNY_DXS(4, 4, 2);
+                else MNI_SKINNY_DXS(4, 2, 2);
+                break;
+            case 8:
+                if (variant == 1) MNI_SKINNY_DXS(8, 2, 1);
+                else if (variant == 2) MNI_SKINNY_DXS(8, 2, 2);
+                else MNI_SKINNY_DXS(8, 1, 2);
+                break;
+            default: return fail(MNI_B200_ERR_ARG, "skinny dx handles at most 8 rows");
+        }
+#undef MNI_SKINNY_DXS
+        MNI_LAUNCH_CHECK("skinny_dx_sliced_kernel");
+        return MNI_B200_OK;
+    }
     const long long rows_per_block = (kDxThreads / 32) * kDxRows;
     const unsigned blocks = static_cast<unsigned>((K + rows_per_block - 1) / rows_per_block);
     const bool full = M == mt && mt >= 4 && N % 512 == 0;   // measured: slower than the guarded loop for 1-2 rows

@@ -1,1 +1,1 @@
-__attribute__((visibility("default"))) const char *mni_b200_build_id(void) { return "29d421111da130e27cca23639209781e1e095b066441c9ff9c1802a2c09eee0b"; }
+__attribute__((visibility("default"))) const char *mni_b200_build_id(void) { return "fa64b4c1b6e8a3e782d74736e3a98263b3216e0a0397f30532bf00d3189130cd"; }

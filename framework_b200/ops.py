@@ -270,6 +270,11 @@ class Linear:
         return dx, dw, dbias
 
 
+def sm_reserve(sms: int) -> None:
+    """Keeps `sms` SMs out of the tensor-core kernels' grids (0 = none): room for a collective that runs beside them."""
+    _lib.check(_lib.lib().mni_b200_sm_reserve(int(sms)))
+
+
 def device_status() -> int:
     """Synchronises the current stream; raises if a kernel recorded a bounded-wait timeout."""
     import ctypes as C

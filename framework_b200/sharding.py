@@ -38,11 +38,16 @@ def panel_bounds(n: int, panels: int, multiple: int = 1) -> List[Tuple[int, int]
     return [(lo, hi) for lo, hi in zip(edges[:-1], edges[1:]) if hi > lo]
 
 
-def reduce_to_root(flat, dst: int = 0, group=None) -> None:
-    """Sums a flat gradient buffer over all ranks onto `dst` (in place on dst)."""
+def reduce_to_root(flat, dst: int = 0, group=None, everywhere: bool = False) -> None:
+    """Sums a flat gradient buffer over all ranks onto `dst` (in place on dst).  With `everywhere` the sum is
+    left on every rank (an all-reduce): what replicas that each apply the optimizer step need, and on NVSwitch
+    systems the form NCCL can reduce inside the switch."""
     import torch.distributed as dist
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.reduce(flat, dst=dst, op=dist.ReduceOp.SUM, group=group)
+        if everywhere:
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+        else:
+            dist.reduce(flat, dst=dst, op=dist.ReduceOp.SUM, group=group)
 
 
 class DataParallelStep:
@@ -57,16 +62,24 @@ class DataParallelStep:
     input_grad()               the shard's input gradient (no exchange)
 
     With `streams` = (main, comm) CUDA streams the reduce overlaps the compute; with None (CPU tests)
-    everything runs in order.  `timeline` (optional) receives (label, event) pairs in issue order.
+    everything runs in order.  `reserve(n)` (optional; `framework_b200.sm_reserve`) is called with
+    `reserve_sms` before the first launch that runs beside a reduce and with 0 after the last: the
+    tensor-core grids are persistent, one CTA per SM, so the collective's CTAs need SMs of their own or
+    they push as many CTAs of the grid into a late second wave.
     """
 
     def __init__(self, forward: Callable[[], None], weight_grad_panels: Sequence[Callable[[], None]],
                  panel_buffers: Sequence, input_grad: Callable[[], None], *, streams=None, dst: int = 0,
-                 group=None, reduce: bool = True):
+                 group=None, reduce: bool = True, everywhere: bool = False,
+                 reserve: Optional[Callable[[int], None]] = None, reserve_sms: int = 0, reserve_forward: bool = False):
         if len(weight_grad_panels) != len(panel_buffers):
             raise ValueError("one flat buffer per weight-gradient panel")
         self.forward, self.panels, self.buffers, self.input_grad = forward, list(weight_grad_panels), list(panel_buffers), input_grad
         self.streams, self.dst, self.group, self.reduce = streams, dst, group, reduce
+        self.reserve = reserve if (reserve is not None and reserve_sms > 0 and reduce) else None
+        self.reserve_sms = reserve_sms
+        self.reserve_forward = reserve_forward      # the reduce may outlast the input gradient: keep the SMs free through the next forward
+        self.everywhere = everywhere
         self._ev_panel: list = []
         self._ev_reduced = None
         if streams is not None:
@@ -80,7 +93,7 @@ class DataParallelStep:
             for fn, buf in zip(self.panels, self.buffers):
                 fn()
                 if self.reduce:
-                    reduce_to_root(buf, self.dst, self.group)
+                    reduce_to_root(buf, self.dst, self.group, self.everywhere)
             self.input_grad()
             return
         import torch
@@ -92,6 +105,8 @@ class DataParallelStep:
             mark("forward done", main)
         if self.reduce:
             main.wait_event(self._ev_reduced)        # the previous step's reduce is done with the gradient buffers
+        if self.reserve:
+            self.reserve(0)                          # nothing runs beside the first weight-gradient panel
         for i, (fn, buf) in enumerate(zip(self.panels, self.buffers)):
             fn()
             if mark:
@@ -103,16 +118,22 @@ class DataParallelStep:
                 comm.wait_event(self._ev_panel[i])
                 if mark:
                     mark(f"reduce {i} begin", comm)
-                reduce_to_root(buf, self.dst, self.group)
+                reduce_to_root(buf, self.dst, self.group, self.everywhere)
                 if mark:
                     mark(f"reduce {i} end", comm)
+            if self.reserve:
+                self.reserve(self.reserve_sms)     # everything launched from here on runs beside a reduce
         if self.reduce:
             self._ev_reduced.record(comm)
         self.input_grad()
+        if self.reserve and not self.reserve_forward:
+            self.reserve(0)
         if mark:
             mark("input grad done", main)
 
     def join(self) -> None:
         """Makes the main stream wait for the last reduce (end of a timed region, or before reading dW)."""
+        if self.reserve:
+            self.reserve(0)
         if self.streams is not None and self.reduce:
             self.streams[0].wait_event(self._ev_reduced)

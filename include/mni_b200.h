@@ -246,6 +246,16 @@ MNI_B200_API int mni_b200_workspace_query(const mni_b200_view *a, const mni_b200
                              size_t *bytes);
 
 /*
+ * Leaves `sms` SMs of the current device out of the tensor-core kernels' persistent grids from now on
+ * (0 = use every SM again).  For a caller that runs something else beside a matmul call -- a collective
+ * that sums the weight gradient over GPUs while the input gradient is computed: the persistent grid is one
+ * CTA per SM with all of its shared memory, so a co-running kernel that takes k SMs would otherwise push k
+ * CTAs of the grid into a second wave that starts when that kernel ends.  (No counterpart in the reference,
+ * which is single-GPU.)
+ */
+MNI_B200_API int mni_b200_sm_reserve(int sms);
+
+/*
  * Synchronises `stream` and reports whether any kernel of this library gave up
  * on a bounded wait since the last call (MNI_B200_ERR_TIMEOUT, with the
  * recorded role/stage word in *detail if detail != NULL).  Clears the record.

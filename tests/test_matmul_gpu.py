@@ -527,3 +527,44 @@ def test_few_rows_many_columns_is_computed_transposed(F, oracle, m, k, n, batch)
     ra, rb = oracle.matmul_backward(H.from_array(g), H.from_array(a), H.from_array(b))
     assert float(np.max(np.abs(da.numpy() - ra.numpy()))) <= tol_3xtf32(n, g, b)
     assert float(np.max(np.abs(db.numpy() - rb.numpy()))) <= tol_3xtf32(m, a, g)
+
+
+@pytest.mark.parametrize("shape_a,shape_b", [((512, 512), (512, 512)), ((1536, 512), (512, 2048)), ((6, 100, 96), (96, 200)),
+                                             ((150, 700), (700, 90)), ((4, 3, 40, 24), (4, 3, 24, 56))])
+def test_independent_pair_launch_of_the_two_gradients(F, oracle, monkeypatch, shape_a, shape_b):
+    """MNI_B200_BWD_PAIR=1: grad_a and grad_b as an independent pair on one stream (the second product skips its
+    dependency wait, runs beside the first and waits for it before it ends).  Called three times in a row with new
+    output gradients, so that a second product that started before its inputs were ready, or a following call that
+    did not wait for the first product, would show."""
+    monkeypatch.setenv("MNI_B200_BWD_PAIR", "1")
+    rng = np.random.default_rng(sum(shape_a))
+    a = rng.standard_normal(shape_a, dtype=np.float32)
+    b = rng.standard_normal(shape_b, dtype=np.float32)
+    for _ in range(3):
+        g = rng.standard_normal(shape_a[:-1] + (shape_b[-1],), dtype=np.float32)
+        _check_bwd(F, oracle, a, b, g, flags=F._lib.FORCE_TENSOR_PATH)
+    _check_bwd(F, oracle, a, b, g, flags=F._lib.FORCE_TENSOR_PATH | F._lib.force_split_k(2))
+    _check_bwd(F, oracle, a, b, g, flags=F._lib.FORCE_TENSOR_PATH | F._lib.FORCE_PACK)
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 1000, 1024), (2, 333, 260), (3, 67, 128), (4, 4096, 4096), (5, 18, 1284),
+                                   (7, 515, 512), (8, 2048, 644), (8, 3, 4), (6, 129, 4100)])
+def test_sliced_streaming_dx_kernel(F, oracle, monkeypatch, m, k, n):
+    """The opt-in dx kernel (a block owns 16 weight rows, each warp a slice of N whose dy values stay in
+    registers): every row count, ragged K and N, accumulation; bit-identical on a second call."""
+    monkeypatch.setenv("MNI_B200_SKINNY_DX_SLICED", "1")
+    rng = np.random.default_rng(700 + m + k + n)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((k, n), dtype=np.float32)
+    dy = rng.standard_normal((m, n), dtype=np.float32)
+    skinny = F._lib.FORCE_SKINNY_PATH
+    for variant in ("0", "1", "2"):
+        monkeypatch.setenv("MNI_B200_DXS_VARIANT", variant)
+        ga, _ = _check_bwd(F, oracle, x, w, dy, flags=skinny)
+        again, _ = _check_bwd(F, oracle, x, w, dy, flags=skinny)
+        assert np.array_equal(ga, again)
+    a0 = rng.standard_normal((m, k), dtype=np.float32)
+    da = _dev(F, a0)
+    F.matmul_backward(_dev(F, dy), _dev(F, x), _dev(F, w), da=da, need_db=False, flags=skinny | F._lib.ACCUMULATE_DA)
+    F.device_status()
+    assert np.max(np.abs(da.numpy() - (a0 + ga))) <= 1e-5 * max(1.0, float(np.max(np.abs(ga))))
