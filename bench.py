@@ -134,6 +134,9 @@ SHARDED = ("c4", "c5a")            # partition across ranks (strong scaling); c2
 # (dram__bytes_read.sum + dram__bytes_write.sum): a cited capture, not a measurement of this run.
 NCU_TRAFFIC = {
     "c2": (34.11e6 + 19.63e6, "profiles/gemm_tc_kernel_c2_linear.md"),
+    # captured on a 1/8 shard (34.7 MB read + 46.3 MB written of 135.3 MB algorithmic; the output's last ~54 MB stay
+    # in L2) and scaled to 64 batches: operands 210.7 MB, output 805.3 MB minus the same L2 residue
+    "c4": (210.7e6 + 805.3e6 - 54.4e6, "profiles/gemm_tc_kernel_c4_broadcast_weight.md (scaled from the 8-batch shard)"),
 }
 C5A_PANELS = 4                      # row panels of dB, each reduced as soon as it is computed
 
@@ -400,6 +403,8 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     base = WORKLOADS[args.workload]
     nccl_ctas = args.nccl_ctas if args.nccl_ctas > 0 else 16
+    if args.sm_reserve < 0:
+        args.sm_reserve = 2 if world >= 8 else 1
     if world > 1:
         # The reduce runs beside persistent one-CTA-per-SM grids: cap the SMs it may take, and leave as many free.
         os.environ.setdefault("NCCL_MAX_CTAS", str(nccl_ctas))
@@ -600,7 +605,8 @@ def run_ours(args):
                                      "note": "sum of algorithmic bytes / sum of the products' stand-alone times"},
                     "peak_source": "measured hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650"}
     else:
-        traffic, source = NCU_TRAFFIC.get(wl.name, (None, None)) if (args.precision != "tf32" and world == 1) else (None, None)
+        traffic, source = (NCU_TRAFFIC.get(wl.name, (None, None))
+                           if (args.precision != "tf32" and world == 1 and args.shard_of == 1) else (None, None))
         issued = first["tflops"] * (1 if args.precision == "tf32" else 3)
         roofline = {"bound": "tensor", "achieved": first["tflops"], "peak": tf32_peak, "unit": "TFLOP/s",
                     "frac": first["tflops"] / tf32_peak, "traffic": traffic,
@@ -960,9 +966,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--nccl-ctas", type=int, default=0,
                     help="cap on the SMs the NCCL reduce may use (NCCL_MAX_CTAS); default 16")
-    ap.add_argument("--sm-reserve", type=int, default=1,
+    ap.add_argument("--sm-reserve", type=int, default=-1,
                     help="1: the GEMMs that run beside the reduce leave that many SMs free; 2: the next forward too; "
-                         "0: they use every SM")
+                         "0: they use every SM; default: 2 from 8 ranks on (the reduce outlasts the input-gradient "
+                         "GEMM there), else 1")
     ap.add_argument("--collective", default="reduce", choices=["reduce", "allreduce"],
                     help="sum of the weight gradient: onto rank 0 (ncclReduce) or onto every rank (ncclAllReduce)")
     ap.add_argument("--shard-of", type=int, default=1,
