@@ -110,7 +110,6 @@ struct KParams {
     FastDiv fd_a_cnt, fd_a_d1, fd_a_d2, fd_b_cnt, fd_b_d1, fd_b_d2;         // batch_coords
     unsigned int *err;
     long long wait_cycles;     // limit of every bounded wait in clock cycles (kWaitCycles unless a test shortens it)
-    int prefetch_dist;         // k-blocks by which the producer's L2 prefetches lead its copies (0 = none)
     int withhold_at;           // test hook: the producer arms its n-th k-block (1-based) but issues no copy for it; 0 = off
     unsigned long long *prof;  // optional role wait counters (null = off)
     // Balanced tail ("stream-K"): tiles [sk_first_tile, tiles) are not dealt out whole; their k-blocks are
@@ -216,13 +215,6 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
         "r"(c4)
         : "memory");
-}
-// Brings a box into L2 only (no shared-memory destination, no barrier): the producer issues these a few
-// k-blocks ahead of the real copies, which then find their data at L2 latency instead of DRAM latency.
-__device__ __forceinline__ void tma_prefetch_5d(const CUtensorMap *map, int c0, int c1, int c2, int c3, int c4) {
-    asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %2, %3, %4, %5}];"
-                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
-                 : "memory");
 }
 __device__ __forceinline__ void tma_store_5d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
@@ -466,17 +458,6 @@ __device__ __forceinline__ void load_operand(int mode, uint32_t dst, const CUten
     }
 }
 
-__device__ __forceinline__ void prefetch_operand(int mode, const CUtensorMap *map, int k0, int row0, int nchunk,
-                                                 int c0, int c1, int c2) {
-    if (mode == kKMajor) {
-        tma_prefetch_5d(map, k0, row0, c2, c1, c0);
-    } else if (mode == kMnSingleBox) {
-        tma_prefetch_5d(map, 0, k0, row0 >> 5, c2, c1);
-    } else {
-        for (int c = 0; c < nchunk; ++c) tma_prefetch_5d(map, row0 + c * 32, k0, c2, c1, c0);
-    }
-}
-
 // CG = 1: one CTA computes a 128 x BN tile.  CG = 2: a pair of CTAs (a 2-CTA cluster) computes a
 // 256 x BN tile with cta_group::2 MMAs issued by the pair's leader; each CTA stages its own 128 rows
 // of A and half (BN/2 rows) of B, so shared-memory and L2 traffic per flop drop by a third.
@@ -590,31 +571,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t dstA = dstA0;
             WorkIter wi = work_begin(p, unit0, unit_step);
             TileCoord t;
-            // Prefetch cursor: walks the same sequence of (unit, k-block) as the copies, p.prefetch_dist k-blocks
-            // ahead, across unit boundaries, and asks the TMA unit to bring each operand box into L2.
-            WorkIter pwi = wi;
-            TileCoord pt;
-            int p_it = 0, p_end = 0, p_lead = 0;
-            bool p_live = p.prefetch_dist > 0;
-            auto prefetch_step = [&]() {
-                if (!p_live) return;
-                if (p_it >= p_end) {
-                    if (!work_next(p, pwi, pt)) { p_live = false; return; }
-                    p_it = pt.it0;
-                    p_end = pt.it1;
-                }
-                int pf = 0, pk = p_it;
-                if (p_it >= p.kiters) { pf = p_it / p.kiters; pk = p_it - pf * p.kiters; }
-                ++p_it;
-                int x0, x1, x2, y0, y1, y2;
-                batch_coords(pt.bt * p.fold + pf, p.a_batch, p.a_d1, p.a_d2, p.fd_a_cnt, p.fd_a_d1, p.fd_a_d2, x0, x1, x2);
-                batch_coords(pt.bt * p.fold + pf, p.b_batch, p.b_d1, p.b_d2, p.fd_b_cnt, p.fd_b_d1, p.fd_b_d2, y0, y1, y2);
-                if (elect_one()) {
-                    prefetch_operand(p.a_mode, &tmA, pk * BK, pt.tm * (BM * CG) + static_cast<int>(cta_rank) * BM, BM / 32, x0, x1, x2);
-                    prefetch_operand(p.b_mode, &tmB, pk * BK, pt.tn * BN + static_cast<int>(cta_rank) * BNL, BNL / 32, y0, y1, y2);
-                }
-            };
-            for (; p_lead < p.prefetch_dist; ++p_lead) prefetch_step();
             while (ok && work_next(p, wi, t)) {
                 int f = 0, kk = t.it0;
                 if (t.it0 >= p.kiters) {
@@ -632,7 +588,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t full = bar_full + 8u * stage;
                     const int k0 = kk * BK;
                     ++armed;
-                    prefetch_step();
                     if (elect_one()) {
                         mbar_arrive_expect_tx(full, RAW_BYTES);
                         if (armed != p.withhold_at) {        // test hook: a stage that is armed and never filled
@@ -1742,9 +1697,6 @@ int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, in
         const long long wc = w && *w ? atoll(w) : 0;
         k.wait_cycles = wc > 0 ? wc : kWaitCycles;
         k.withhold_at = k.wait_cycles <= 200000000LL ? env_int("MNI_B200_TEST_WITHHOLD_KBLOCK", 0) : 0;
-        // L2 prefetch distance (MNI_B200_L2_PREFETCH; default: narrow tiles only, see make_plan's comment on them)
-        const int pf_env = env_int("MNI_B200_L2_PREFETCH", -1);
-        k.prefetch_dist = pf_env >= 0 ? pf_env : (pl.bn <= 128 ? 12 : 0);
     }
     k.prof = env_int("MNI_B200_ROLE_WAITS", 0) ? role_wait_ptr() : nullptr;
     k.sk = pl.sk ? 1 : 0;
