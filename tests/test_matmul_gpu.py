@@ -568,3 +568,51 @@ def test_sliced_streaming_dx_kernel(F, oracle, monkeypatch, m, k, n):
     F.matmul_backward(_dev(F, dy), _dev(F, x), _dev(F, w), da=da, need_db=False, flags=skinny | F._lib.ACCUMULATE_DA)
     F.device_status()
     assert np.max(np.abs(da.numpy() - (a0 + ga))) <= 1e-5 * max(1.0, float(np.max(np.abs(ga))))
+
+
+def test_sm_reservation_leaves_results_unchanged(F, oracle):
+    """mni_b200_sm_reserve keeps SMs out of the persistent grids (room for a collective that runs beside a
+    product): plans change (fewer slots, other splits / tails), results must not, and 0 restores the full grid."""
+    rng = np.random.default_rng(91)
+    shapes = [((1536, 512), (512, 2048)), ((6, 100, 96), (96, 200)), ((512, 512), (512, 512)), ((300, 72), (72, 260))]
+    try:
+        for reserve in (16, 64, 0):
+            F.sm_reserve(reserve)
+            for sa, sb in shapes:
+                a = rng.standard_normal(sa, dtype=np.float32)
+                b = rng.standard_normal(sb, dtype=np.float32)
+                g = rng.standard_normal(sa[:-1] + (sb[-1],), dtype=np.float32)
+                _check_fwd(F, oracle, a, b, flags=F._lib.FORCE_TENSOR_PATH)
+                _check_bwd(F, oracle, a, b, g, flags=F._lib.FORCE_TENSOR_PATH)
+    finally:
+        F.sm_reserve(0)
+    with pytest.raises(F._lib.MniError):
+        F.sm_reserve(-1)
+
+
+def test_weight_gradient_in_row_panels_through_narrow_views(F, oracle):
+    """What the row-sharded square problem does for its pipelined reduce: rows [lo, hi) of dB = A[:, lo:hi]^T . dC,
+    with the column panel of A and the row panel of B passed as views of the same storage (pointer offset + same
+    strides) and each panel's result landing in its rows of ONE flat buffer."""
+    import torch
+    from framework_b200.sharding import panel_bounds
+    rng = np.random.default_rng(92)
+    m, k, n = 384, 640, 320
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    g = rng.standard_normal((m, n), dtype=np.float32)
+    H = oracle.HostTensor
+    _, ref_db = oracle.matmul_backward(H.from_array(g), H.from_array(a), H.from_array(b))
+    ad, bd, gd = _dev(F, a), _dev(F, b), _dev(F, g)
+    flat = torch.full((k * n,), float("nan"), device="cuda")
+    for lo, hi in panel_bounds(k, 3, multiple=128):
+        a_cols, b_rows = ad.narrow(1, lo, hi - lo), bd.narrow(0, lo, hi - lo)
+        assert a_cols.ptr == ad.ptr + 4 * lo and a_cols.strides == ad.strides and not a_cols.is_contiguous()
+        assert b_rows.is_contiguous()
+        F.matmul_backward(gd, a_cols, b_rows, need_da=False, db=F.DeviceTensor(flat[lo * n:hi * n], (hi - lo, n)))
+    F.device_status()
+    got = flat.cpu().numpy().reshape(k, n)
+    assert float(np.max(np.abs(got - ref_db.numpy()))) <= tol_3xtf32(m, a, g)
+    assert rel_fro(got, ref_db.numpy()) <= regression_bound_3xtf32(m)
+    with pytest.raises(ValueError):
+        ad.narrow(1, 600, 100)

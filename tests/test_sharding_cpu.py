@@ -112,3 +112,20 @@ def test_two_gloo_ranks_reproduce_the_unsharded_result(a_shape, w_shape):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert results == {0: True, 1: True}
+
+
+def test_step_driver_reserves_sms_only_beside_a_reduce():
+    """The driver asks for free SMs after it has issued a reduce and gives them back before the next first
+    weight-gradient panel (or, with `reserve_forward` off, right after the input gradient).  Run without a
+    process group: the collective is a no-op, the order of calls is what is checked."""
+    if not torch.cuda.is_available():
+        # streams=None path: no reservation is ever requested on the in-order path
+        calls = []
+        step = DataParallelStep(lambda: calls.append("fwd"), [lambda: calls.append("dW0"), lambda: calls.append("dW1")],
+                                [torch.zeros(4), torch.zeros(4)], lambda: calls.append("dx"), streams=None,
+                                reserve=lambda n: calls.append(("reserve", n)), reserve_sms=16)
+        step()
+        step.join()
+        assert [c for c in calls if isinstance(c, str)] == ["fwd", "dW0", "dW1", "dx"]
+        assert calls[-1] == ("reserve", 0)                    # join always hands the SMs back
+        assert ("reserve", 16) not in calls
