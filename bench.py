@@ -402,7 +402,7 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     base = WORKLOADS[args.workload]
-    nccl_ctas = args.nccl_ctas if args.nccl_ctas > 0 else (32 if base.name == "c5a" else 16)
+    nccl_ctas = args.nccl_ctas if args.nccl_ctas > 0 else (32 if (base.name == "c5a" and world >= 8) else 16)
     if args.sm_reserve < 0:
         args.sm_reserve = 2 if world >= 8 else 1
     if world > 1:
@@ -965,7 +965,7 @@ def main():
                     help="replay the step from a CUDA graph (auto: only for steps under 0.2 ms)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--nccl-ctas", type=int, default=0,
-                    help="cap on the SMs the NCCL reduce may use (NCCL_MAX_CTAS); default 16, 32 for c5a's 268 MB")
+                    help="cap on the SMs the NCCL reduce may use (NCCL_MAX_CTAS); default 16 (32 for c5a's 268 MB at 8 ranks: measured 1883 vs 1775 TFLOP/s there, but 936 vs 1001 at 4 ranks and 463 vs 502 at 2)")
     ap.add_argument("--sm-reserve", type=int, default=-1,
                     help="1: the GEMMs that run beside the reduce leave that many SMs free; 2: the next forward too; "
                          "0: they use every SM; default: 2 from 8 ranks on (the reduce outlasts the input-gradient "
