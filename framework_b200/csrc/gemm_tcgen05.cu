@@ -397,6 +397,20 @@ __device__ __forceinline__ WorkIter work_begin(const KParams &p, int slot, int n
     return wi;
 }
 __device__ __forceinline__ TileCoord decode_unit(const KParams &p, int unit);
+// Cuts a long unit into equal pieces of at most p.chunk_iters k-blocks: `t` becomes the first piece, the iterator
+// remembers the rest.
+__device__ __forceinline__ void first_piece(const KParams &p, WorkIter &wi, TileCoord &t) {
+    const int len = t.it1 - t.it0;
+    if (p.chunk_iters > 0 && len > p.chunk_iters + (p.chunk_iters >> 1)) {
+        const int pieces = (len + p.chunk_iters - 1) / p.chunk_iters;
+        wi.cur = t;
+        wi.piece_len = (len + pieces - 1) / pieces;
+        wi.piece_end = t.it1;
+        wi.piece_no = 0;
+        t.it1 = t.it0 + wi.piece_len;
+        wi.piece_it = t.it1;
+    }
+}
 __device__ __forceinline__ bool work_next(const KParams &p, WorkIter &wi, TileCoord &t) {
     if (wi.piece_it < wi.piece_end) {          // next piece of the current unit
         t = wi.cur;
@@ -409,16 +423,7 @@ __device__ __forceinline__ bool work_next(const KParams &p, WorkIter &wi, TileCo
     if (wi.unit < wi.unit_end) {
         t = decode_unit(p, wi.unit);
         wi.unit += wi.unit_step;
-        const int len = t.it1 - t.it0;
-        if (p.chunk_iters > 0 && len > p.chunk_iters + (p.chunk_iters >> 1)) {
-            const int pieces = (len + p.chunk_iters - 1) / p.chunk_iters;
-            wi.cur = t;
-            wi.piece_len = (len + pieces - 1) / pieces;      // equal pieces
-            wi.piece_end = t.it1;
-            wi.piece_no = 0;
-            t.it1 = t.it0 + wi.piece_len;
-            wi.piece_it = t.it1;
-        }
+        first_piece(p, wi, t);
         return true;
     }
     if (wi.w < wi.w1) {
@@ -432,6 +437,9 @@ __device__ __forceinline__ bool work_next(const KParams &p, WorkIter &wi, TileCo
         t.shared = (it0 != 0 || it1 != per_tile) ? 1 : 0;
         t.park = wi.w == wi.w0 ? 0 : 1;
         wi.w += it1 - it0;
+        // A whole tile inside a tail range is summed in pieces like any other unit; a cut tile is not (its one
+        // accumulator is what gets parked or reduced), so its chain is as long as its share of the contraction.
+        if (!t.shared) first_piece(p, wi, t);
         return true;
     }
     return false;

@@ -616,3 +616,40 @@ def test_weight_gradient_in_row_panels_through_narrow_views(F, oracle):
     assert rel_fro(got, ref_db.numpy()) <= regression_bound_3xtf32(m)
     with pytest.raises(ValueError):
         ad.narrow(1, 600, 100)
+
+
+def test_balanced_tail_with_a_long_contraction(F, oracle, monkeypatch):
+    """Tail ranges longer than a tile (K = 2048, 90 pair-tiles on 74 pairs): the whole tiles inside a range are summed
+    in pieces like every other unit, the cut ones in one accumulator each.  Acceptance bound, and a relative error
+    bound that allows for a cut tile's longer chain (the accumulate truncates: ~7e-9 per contraction element)."""
+    monkeypatch.setenv("MNI_B200_STREAMK", "1")
+    rng = np.random.default_rng(93)
+    a = rng.standard_normal((2560, 2048), dtype=np.float32)
+    b = rng.standard_normal((2048, 2304), dtype=np.float32)
+    H = oracle.HostTensor
+    ref = oracle.matmul(H.from_array(a), H.from_array(b)).numpy()
+    first = F.matmul(_dev(F, a), _dev(F, b)).numpy()
+    again = F.matmul(_dev(F, a), _dev(F, b)).numpy()
+    F.device_status()
+    assert np.array_equal(first, again)
+    assert float(np.max(np.abs(first - ref))) <= tol_3xtf32(2048, a, b)
+    assert rel_fro(first, ref) <= 5e-6 + 1e-8 * 2048
+
+
+def test_shard_of_the_broadcast_weight_problem_takes_the_default_tail(F, oracle):
+    """One rank's share of an 8-rank run of the broadcast-weight configuration ([8,1024,768].[768,3072]): its input
+    gradient has 96 pair-tiles for 74 pairs, which the default policy runs with the balanced tail.  First and last
+    128 rows of dA against the CPU backend."""
+    rng = np.random.default_rng(94)
+    a = rng.standard_normal((8, 1024, 768), dtype=np.float32)
+    w = (0.02 * rng.standard_normal((768, 3072))).astype(np.float32)
+    g = rng.standard_normal((8, 1024, 3072), dtype=np.float32)
+    da, _ = F.matmul_backward(_dev(F, g), _dev(F, a), _dev(F, w))
+    F.device_status()
+    da = da.numpy()
+    H = oracle.HostTensor
+    wt = oracle.permute(H.from_array(w), [1, 0])
+    for bt, rows in ((0, slice(0, 128)), (7, slice(896, 1024))):
+        ref = oracle.matmul(H.from_array(g[bt, rows]), wt).numpy()
+        assert float(np.max(np.abs(da[bt, rows] - ref))) <= tol_3xtf32(3072, g, w)
+        assert rel_fro(da[bt, rows], ref) <= 5e-6 + 1e-8 * 3072
