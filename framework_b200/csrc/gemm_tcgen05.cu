@@ -27,13 +27,18 @@
 //               pitch is not a multiple of 16 bytes take a plain-store fallback.
 //
 // CG = 2: two CTAs of a cluster share a 256 x BN tile (cta_group::2 MMAs issued by the leader).
-// Work is dealt out as whole tiles, round-robin over the CTAs (pairs); a ragged last wave is cut
+// Work is dealt out as whole tiles, round-robin over the CTAs (pairs); a badly ragged last wave is cut
 // into equal ranges of k-blocks instead, and a tile shared by several CTAs is summed in slot order
-// by the CTA that holds its first k-blocks (flags in global memory, bounded waits).
+// by whichever of them finishes last (tickets and flags in global memory, bounded waits).
 //
-// Every wait on an mbarrier or flag is bounded: after ~2 s worth of clock cycles the waiter
-// records a code in a global error word, raises a CTA-wide abort flag and all roles
-// drain to the common exit, where TMEM is released.  Nothing traps.
+// The tensor core's f32 accumulate rounds toward zero (measured: 2.35e-9 * K relative per chain, three
+// chains' worth in 3xTF32), so a long contraction is not summed in one accumulator: a unit is handed
+// out in pieces of at most KParams::chunk_iters k-blocks, each piece gets a fresh accumulator, and the
+// epilogue adds the later pieces to the output with ordered TMA reduce-adds (fixed order: reproducible).
+//
+// Every wait on an mbarrier or flag is bounded: after KParams::wait_cycles clock cycles (~2 s unless a
+// test shortens it) the waiter records a code in a global error word, raises a CTA-wide abort flag and
+// all roles drain to the common exit, where TMEM is released.  Nothing traps.
 #include "internal.h"
 
 #include <string.h>
