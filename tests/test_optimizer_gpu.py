@@ -86,6 +86,9 @@ def test_adamw_bias_correction_at_large_steps(F, oracle, step):
     v = np.abs(0.01 * rng.standard_normal(n)).astype(np.float32)
     cfg = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=step)
     dw, dm, dv, dg = (_dev(F, a) for a in (w, m, v, g))
+    scratch = [_dev(F, np.zeros(8, np.float32)) for _ in range(4)]
+    F.adamw_step(*scratch, lr=1e-3, step=1)          # first launch of the kernel loads its module: keep that out of the timing
+    F.device_status()
     t0 = time.perf_counter()
     F.adamw_step(dw, dm, dv, dg, **cfg)
     host_s = time.perf_counter() - t0
