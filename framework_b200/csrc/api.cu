@@ -124,8 +124,18 @@ int device_state(DeviceState **out) {
     return MNI_B200_OK;
 }
 
+// True while `stream` records into a CUDA graph.
+bool stream_is_capturing(cudaStream_t stream) {
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &status) != cudaSuccess) {
+        cudaGetLastError();   // the legacy stream beside another stream's capture: not capturing itself
+        return false;
+    }
+    return status != cudaStreamCaptureStatusNone;
+}
+
 // Makes `bytes` of scratch available and returns its base.
-int scratch_base(DeviceState &st, size_t bytes, uint8_t **base) {
+int scratch_base(DeviceState &st, size_t bytes, cudaStream_t stream, uint8_t **base) {
     if (st.user_ws) {
         if (bytes > st.user_bytes)
             return fail(MNI_B200_ERR_WORKSPACE, "caller-provided scratch holds %zu bytes, %zu needed", st.user_bytes,
@@ -135,6 +145,13 @@ int scratch_base(DeviceState &st, size_t bytes, uint8_t **base) {
     }
     if (bytes > st.ws_bytes) {
         const size_t want = bytes + bytes / 4 + (1u << 20);
+        // Growing frees the old buffer, which a capturing stream must not do (it would end the capture in
+        // an error) and which would leave the nodes already recorded with a dangling address.
+        if (st.ws && stream_is_capturing(stream))
+            return fail(MNI_B200_ERR_WORKSPACE,
+                        "scratch would have to grow from %zu to %zu bytes while the stream is capturing: run the call "
+                        "once before the capture, or hand the library a buffer (mni_b200_workspace_set)",
+                        st.ws_bytes, bytes);
         if (st.ws) {
             // cudaFree waits for work that may still read the old buffer.
             cudaError_t e = cudaFree(st.ws);
@@ -654,7 +671,7 @@ int with_scratch(uint32_t flags, void *stream, Body body) {
     Call real;
     real.st = st; real.arena.st = st; real.arena.dry = false; real.stream = static_cast<cudaStream_t>(stream); real.flags = flags;
     if (dry.arena.used > 0) {
-        rc = scratch_base(*st, dry.arena.used, &real.base);
+        rc = scratch_base(*st, dry.arena.used, real.stream, &real.base);
         if (rc) return rc;
     }
     rc = body(real);

@@ -1492,13 +1492,19 @@ uint32_t desc_hi_bits(uint32_t sbo_bytes, uint32_t layout_type) {
 template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false, bool SK = false>
 cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
                            const CUtensorMap &tmD, const KParams &k, cudaStream_t stream) {
-    static std::once_flag once;
-    static cudaError_t attr = cudaSuccess;
-    std::call_once(once, [] {
+    // The shared-memory opt-in is an attribute of the function on ONE device: set once per device of the process
+    // (a bit per device ordinal; setting it twice from two threads is harmless).
+    static std::atomic<uint64_t> opted_in{0};
+    int dev = 0;
+    cudaError_t attr = cudaGetDevice(&dev);
+    if (attr != cudaSuccess) return attr;
+    const uint64_t bit = 1ull << (dev & 63);
+    if ((opted_in.load(std::memory_order_acquire) & bit) == 0) {
         attr = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FAST, NS, CG, TA, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024);
-    });
-    if (attr != cudaSuccess) return attr;
+        if (attr != cudaSuccess) return attr;
+        opted_in.fetch_or(bit, std::memory_order_release);
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(pl.grid));
     cfg.blockDim = dim3(32 * (2 + NS + kEpiWarps));

@@ -240,6 +240,15 @@ MNI_B200_API int mni_b200_contiguous(const mni_b200_view *src, float *dst, void 
  * gathered first); and the pointwise entry points (add_bias_bwd, bias_gelu_bwd,
  * grad_sumsq) applied to tensors no larger than a, b or the forward output.
  * The flags given are the flags the later calls must use.
+ *
+ * CUDA graphs.  Every call may be recorded by a capturing stream (the side stream
+ * is forked and joined with events, which capture follows).  The recorded nodes
+ * hold the scratch address of the moment: a library-owned buffer that grows later
+ * is freed and leaves such a graph with a dangling address, and it cannot grow
+ * during a capture at all (the call then fails with MNI_B200_ERR_WORKSPACE and
+ * records nothing).  A caller that replays graphs hands the library a buffer of
+ * the queried size with mni_b200_workspace_set and keeps it for the graph's life,
+ * or runs each captured call once beforehand and makes no larger call afterwards.
  */
 MNI_B200_API int mni_b200_workspace_set(void *ptr, size_t bytes);
 MNI_B200_API int mni_b200_workspace_query(const mni_b200_view *a, const mni_b200_view *b, uint32_t flags,

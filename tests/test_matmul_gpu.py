@@ -441,6 +441,46 @@ def test_small_backward_side_stream_inside_a_cuda_graph(F, oracle):
     F.device_status()
 
 
+def test_scratch_growth_is_refused_while_a_stream_captures(F, oracle):
+    """Growing the library-owned scratch frees the old buffer, which a capturing stream must not do and which
+    would leave recorded nodes with a dangling address.  A call that would need it during a capture fails with
+    MNI_B200_ERR_WORKSPACE before anything is recorded, the capture itself stays valid, and the same call run
+    eagerly afterwards grows the scratch and is correct."""
+    import torch
+    lib = F._lib.lib()
+    rng = np.random.default_rng(33)
+    small_a = rng.standard_normal((128, 256), dtype=np.float32)
+    small_b = rng.standard_normal((256, 128), dtype=np.float32)
+    a = rng.standard_normal((1024, 2048), dtype=np.float32)
+    b = rng.standard_normal((2048, 1024), dtype=np.float32)
+    sa, sb, ad, bd = (F.DeviceTensor.from_numpy(x) for x in (small_a, small_b, a, b))
+    split = F._lib.FORCE_TENSOR_PATH | F._lib.force_split_k(4)
+    torch.cuda.synchronize()
+    F._lib.check(lib.mni_b200_release())                 # start from no scratch at all
+    small = F.matmul(sa, sb, flags=split)                # 4 x 64 KiB of partial sums: a small buffer now exists
+    out = F.DeviceTensor.empty((1024, 1024))
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            F.matmul(sa, sb, out=small, flags=split)     # fits: recorded
+            with pytest.raises(F._lib.MniError) as ei:   # 4 x 4 MiB of partial sums: would have to grow
+                F.matmul(ad, bd, out=out, flags=split)
+    assert ei.value.status == 7, ei.value                # MNI_B200_ERR_WORKSPACE
+    assert "capturing" in ei.value.message
+    small.storage.zero_()
+    graph.replay()                                       # the capture survived the refused call
+    torch.cuda.synchronize()
+    H = oracle.HostTensor
+    ref_small = oracle.matmul(H.from_array(small_a), H.from_array(small_b)).numpy()
+    assert np.max(np.abs(small.numpy() - ref_small)) <= tol_3xtf32(256, small_a, small_b)
+    F.matmul(ad, bd, out=out, flags=split)               # eager: grows and runs
+    ref = oracle.matmul(H.from_array(a), H.from_array(b)).numpy()
+    assert np.max(np.abs(out.numpy() - ref)) <= tol_3xtf32(2048, a, b)
+    F.device_status()
+
+
 @pytest.mark.parametrize("shape_a,shape_b,flags,bias", [
     ((1536, 512), (512, 2048), 0, False),            # 48 pair-tiles on 74 pairs: every tile is cut 2-3 ways
     ((2560, 1024), (1024, 2304), 0, True),           # one whole round, then a 16-tile tail dealt out by k-blocks
