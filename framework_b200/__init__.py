@@ -8,9 +8,9 @@ from . import _lib  # noqa: F401
 from .ops import (  # noqa: F401
     Linear, adamw_step, add, add_backward, bias_gelu, bias_gelu_backward, broadcast_shape, clip_and_step,
     device_status, grad_norm, launch_count, matmul, matmul_backward, matmul_bias_gelu, permute, permute_backward,
-    sm_reserve, softmax, softmax_backward,
+    plan_describe, sm_reserve, softmax, softmax_backward,
 )
 from .tensor import DeviceTensor  # noqa: F401
 
 __all__ = ["DeviceTensor", "Linear", "adamw_step", "add", "add_backward", "bias_gelu", "bias_gelu_backward",
-           "broadcast_shape", "clip_and_step", "device_status", "grad_norm", "launch_count", "matmul", "matmul_backward", "matmul_bias_gelu", "permute", "permute_backward", "sm_reserve", "softmax", "softmax_backward"]
+           "broadcast_shape", "clip_and_step", "device_status", "grad_norm", "launch_count", "matmul", "matmul_backward", "matmul_bias_gelu", "permute", "permute_backward", "plan_describe", "sm_reserve", "softmax", "softmax_backward"]

@@ -74,6 +74,8 @@ _SIGNATURES = {
     "mni_b200_sm_reserve": (C.c_int, [C.c_int]),
     "mni_b200_workspace_set": (C.c_int, [C.c_void_p, C.c_size_t]),
     "mni_b200_workspace_query": (C.c_int, [C.POINTER(View), C.POINTER(View), C.c_uint32, C.POINTER(C.c_size_t)]),
+    "mni_b200_plan_describe": (C.c_int, [C.POINTER(View), C.POINTER(View), C.c_int, C.c_uint32, C.c_int, C.c_char_p,
+                                         C.c_size_t]),
     "mni_b200_device_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "mni_b200_launch_count": (C.c_uint64, []),
     "mni_b200_release": (C.c_int, []),

@@ -10,6 +10,7 @@
 
 #include <algorithm>
 #include <mutex>
+#include <string>
 #include <vector>
 
 namespace mni {
@@ -263,6 +264,11 @@ struct Call {
     int flag_bank = 0;         // 1 while launches go to the library's side stream / for the second product of a pair
     int dep_mode = 0;          // GemmProblem::dep_mode of the tensor-path launches issued now
     int sm_share = 1;          // 2 while grad_a and grad_b run side by side: each is planned for half of the SMs
+    std::string *plan_log = nullptr;   // mni_b200_plan_describe: one line per launch the call would make
+    const char *label = "";            // which product the launches logged now belong to
+    void note(const std::string &what) const {
+        if (plan_log) *plan_log += std::string(label) + what + "\n";
+    }
     // SMs the persistent tensor-core grids are planned for: all of them minus the caller's reservation, divided
     // between the products that run at the same time (kept even, CTA pairs take two)
     int gemm_sms() const { return std::max(8, ((st->sm_count - st->sm_reserve) / sm_share) & ~1); }
@@ -283,6 +289,7 @@ int pack_view(Call &c, const mni_b200_view &v, mni_b200_view *packed, size_t *of
     packed->shape[0] = batch; packed->shape[1] = rows; packed->shape[2] = cols;
     packed->stride[0] = rows * ld; packed->stride[1] = ld; packed->stride[2] = 1;
     packed->ptr = c.dry() ? reinterpret_cast<const float *>(static_cast<uintptr_t>(256)) : c.at(off);
+    c.note("gather of a strided operand into scratch");
     if (c.dry()) return MNI_B200_OK;
     return launch_pack(v, c.at(off), ld, c.stream);
 }
@@ -312,6 +319,7 @@ int run_gemm(Call &c, GemmProblem &p) {
     const size_t pbytes = gemm_tc_partial_bytes(p, c.gemm_sms());
     size_t poff = 0;
     if (pbytes) poff = c.arena.reserve(pbytes);
+    if (c.plan_log) c.note(gemm_tc_describe(p, c.gemm_sms()));
     if (c.dry()) return MNI_B200_OK;
     return launch_gemm_tc(p, pbytes ? c.at(poff) : nullptr, c.st->err_word, c.gemm_sms(), c.stream);
 }
@@ -359,6 +367,7 @@ int fwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, float *out
     if (s.batch * s.M * s.N == 0) return MNI_B200_OK;
     if (s.K == 0) return zero_or_bias_fill(c, out, s.batch * s.M, s.N, bias, accumulate);
 
+    if (!*c.label) c.label = "forward: ";
     const bool want_skinny = (c.flags & MNI_B200_FORCE_SKINNY_PATH) != 0 ||
                              ((c.flags & MNI_B200_FORCE_TENSOR_PATH) == 0 && s.M <= skinny_fwd_row_limit(s.N));
     if (want_skinny && s.batch == 1 && skinny_fwd_supported(s.M, s.N, s.K)) {
@@ -369,6 +378,7 @@ int fwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, float *out
         if (a_ok && b_ok) {
             const size_t pbytes = skinny_fwd_partial_bytes(s.M, s.N, s.K, c.st->sm_count);
             const size_t poff = c.arena.reserve(pbytes);
+            c.note("streaming (skinny) forward kernel");
             if (c.dry()) return MNI_B200_OK;
             const int64_t ldw = s.K == 1 ? round_up(s.N, 4) : b->stride[bn - 2];
             return launch_skinny_fwd(a->ptr, a->stride[an - 2], b->ptr, ldw, out, s.N, bias, accumulate, s.M, s.N,
@@ -477,6 +487,7 @@ int grad_gemm(Call &c, Operand X, Operand Y, int64_t R, int64_t Cn, int64_t kdim
     p.C = c.dry() ? nullptr : c.at(off);
     p.ldc = Cn; p.c_bstride = R * Cn; p.accumulate = false;
     int rc = run_gemm(c, p);
+    c.note("sum over the broadcast batch dims (unbroadcast kernel)");
     if (rc || c.dry()) return rc;
     int64_t gshape[MNI_B200_MAX_DIMS + 2];
     for (int i = 0; i < onb; ++i) gshape[i] = ob[i];
@@ -550,14 +561,18 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
             c.flag_bank = 0;
             c.dep_mode = 0;
             c.sm_share = 1;
+            c.label = "";
             if (!on) return;
             c.stream = main;
             if (cudaEventRecord(c.st->ev_join, c.st->side) == cudaSuccess) cudaStreamWaitEvent(main, c.st->ev_join, 0);
         }
     } join{c, main_stream, fork};
 
+    if (share_sms) c.note("grad_a and grad_b side by side, each planned for half of the SMs");
+    else if (overlap) c.note("grad_b on the side stream beside grad_a");
     if (dbias) {
         // Column sums over every row of dc (ops/elementwise.rs:224-229 via utils::unbroadcast).
+        c.label = "grad_bias: ";
         if (side_dbias && !c.dry()) c.stream = c.st->side;
         const int64_t rows = g_batch * s.M;
         if (rows == 0 || s.N == 0) {
@@ -584,6 +599,7 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
             }
             const size_t pbytes = colsum_partial_bytes(rows, s.N, c.st->sm_count);
             const size_t poff = c.arena.reserve(pbytes);
+            c.note(side_dbias ? "column sums, on the side stream" : "column sums");
             if (!c.dry()) {
                 rc = launch_colsum(src, ld, dbias, rows, s.N, acc_dbias, c.at(poff), c.st->sm_count, c.stream);
                 if (rc) return rc;
@@ -594,11 +610,13 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
     c.stream = main_stream;
 
     // grad_a = unbroadcast(dc . b^T, a.shape)   (ops/matmul.rs:231-240)
+    c.label = "grad_a: ";
     if (da && a_elems > 0) {
         if (!da_wanted) {
             rc = zero_or_bias_fill(c, da, a_elems, 1, nullptr, acc_da);
             if (rc) return rc;
         } else if (skinny_dx) {
+            c.note("streaming (skinny) input-gradient kernel");
             if (!c.dry()) {
                 rc = launch_skinny_dx(dc->ptr, dc->stride[gn - 2], b->ptr, b->stride[b->ndim - 2], da, s.K, acc_da,
                                       s.M, s.N, s.K, c.stream);
@@ -624,11 +642,13 @@ int bwd_body(Call &c, const mni_b200_view *a, const mni_b200_view *b, const mni_
 
     // grad_b = unbroadcast(a^T . dc, b.shape)   (ops/matmul.rs:242-251)
     if (overlap) { if (!c.dry()) c.stream = c.st->side; c.flag_bank = 1; }
+    c.label = "grad_b: ";
     if (db && b_elems > 0) {
         if (!db_wanted) {
             rc = zero_or_bias_fill(c, db, b_elems, 1, nullptr, acc_db);
             if (rc) return rc;
         } else if (skinny_dw) {
+            c.note("streaming (skinny) weight-gradient kernel");
             if (!c.dry()) {
                 rc = launch_skinny_dw(a->ptr, a->stride[a->ndim - 2], dc->ptr, dc->stride[gn - 2], db, s.N, acc_db,
                                       s.M, s.N, s.K, c.stream);
@@ -939,6 +959,41 @@ int mni_b200_workspace_query(const mni_b200_view *a, const mni_b200_view *b, uin
     const int64_t biggest = std::max({s.a_batch * s.M * s.K, s.b_batch * s.K * s.N, rows * s.N, int64_t{1}});
     need = std::max(need, (sumsq_partial_bytes(biggest, st->sm_count) + 255) & ~static_cast<size_t>(255));
     *bytes = need;
+    return MNI_B200_OK;
+}
+
+int mni_b200_plan_describe(const mni_b200_view *a, const mni_b200_view *b, int backward, uint32_t flags, int sm_count,
+                           char *out, size_t out_len) {
+    if (!out || out_len == 0) return fail(MNI_B200_ERR_ARG, "out is null or empty");
+    if (sm_count < 8 || sm_count > 4096) return fail(MNI_B200_ERR_ARG, "sm_count %d out of range", sm_count);
+    out[0] = 0;
+    Shapes s;
+    int rc = analyse(a, b, s);
+    if (rc) return rc;
+    // A stand-in for the device: the plans depend on its SM count only.
+    DeviceState st;
+    st.sm_count = sm_count;
+    std::string log;
+    Call c;
+    c.st = &st; c.arena.dry = true; c.stream = nullptr; c.flags = flags; c.plan_log = &log;
+    float *fake = reinterpret_cast<float *>(static_cast<uintptr_t>(256));
+    if (!backward) {
+        rc = fwd_body(c, a, b, fake, nullptr);
+    } else {
+        // the forward output's gradient: contiguous, broadcast batch + [M, N]
+        mni_b200_view dc{};
+        dc.ptr = fake;
+        dc.ndim = s.out_nb + 2;
+        for (int i = 0; i < s.out_nb; ++i) dc.shape[i] = s.out_batch[i];
+        dc.shape[s.out_nb] = s.M; dc.shape[s.out_nb + 1] = s.N;
+        int64_t acc = 1;
+        for (int d = dc.ndim - 1; d >= 0; --d) { dc.stride[d] = acc; acc *= dc.shape[d]; }
+        rc = bwd_body(c, a, b, &dc, fake, fake, backward > 1 ? fake : nullptr);
+    }
+    if (rc) return rc;
+    if (log.size() + 1 > out_len)
+        return fail(MNI_B200_ERR_ARG, "the description needs %zu bytes, %zu given", log.size() + 1, out_len);
+    memcpy(out, log.c_str(), log.size() + 1);
     return MNI_B200_OK;
 }
 

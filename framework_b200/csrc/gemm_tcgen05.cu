@@ -41,6 +41,7 @@
 // all roles drain to the common exit, where TMEM is released.  Nothing traps.
 #include "internal.h"
 
+#include <stdio.h>
 #include <string.h>
 
 #include <algorithm>
@@ -1600,6 +1601,27 @@ size_t gemm_tc_partial_bytes(const GemmProblem &p0, int sm_count) {
     if (pl.sk) return static_cast<size_t>(pl.grid) * 2 * BM * pl.bn * sizeof(float);   // two parked accumulators per CTA
     if (pl.splits <= 1) return 0;
     return static_cast<size_t>(pl.splits) * p.batch * p.M * p.N * sizeof(float);
+}
+
+std::string gemm_tc_describe(const GemmProblem &p0, int sm_count) {
+    bool transposed = false;
+    const GemmProblem p = kernel_view(p0, &transposed);
+    const Plan pl = make_plan(p, sm_count);
+    const int chunk_k = env_int("MNI_B200_CHUNK_K", 1024);
+    // pieces a whole unit's contraction is summed in (the kernel's first_piece rule)
+    const long long iters = p.fold * ((p.K + pl.bk - 1) / pl.bk);
+    const long long len = (iters + pl.splits - 1) / pl.splits;
+    const long long ci = (chunk_k > 0 && p.D == nullptr) ? std::max(1, chunk_k / pl.bk) : 0;
+    const int pieces = (ci > 0 && len > ci + ci / 2) ? static_cast<int>((len + ci - 1) / ci) : 1;
+    char buf[320];
+    snprintf(buf, sizeof(buf),
+             "tensor m=%lld n=%lld k=%lld batch=%lld fold=%lld bn=%d bk=%d pair=%d tmem_a=%d stages=%d splits=%d "
+             "tail=%d grid=%d exchanged=%d single_pass=%d pieces=%d",
+             static_cast<long long>(p.M), static_cast<long long>(p.N), static_cast<long long>(p.K),
+             static_cast<long long>(p.batch), static_cast<long long>(p.fold), pl.bn, pl.bk, pl.cg == 2 ? 1 : 0,
+             pl.ta ? 1 : 0, pl.stages, pl.splits, pl.sk ? 1 : 0, pl.grid, transposed ? 1 : 0, p.fast_tf32 ? 1 : 0,
+             pieces);
+    return buf;
 }
 
 int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, int sm_count,

@@ -105,13 +105,6 @@ struct GemmProblem {
     float *D = nullptr;
 };
 
-// Scratch layout handed to launchers (all device memory, owned by api.cu).
-struct Scratch {
-    uint8_t *base = nullptr;
-    size_t bytes = 0;
-    uint32_t *err_word = nullptr;  // device-side timeout record (inside base)
-};
-
 // Bytes of split-K partial storage launch_gemm_tc would use for this problem (0 if none).
 size_t gemm_tc_partial_bytes(const GemmProblem &p, int sm_count);
 
@@ -119,6 +112,9 @@ size_t gemm_tc_partial_bytes(const GemmProblem &p, int sm_count);
 // `partial` must hold gemm_tc_partial_bytes() bytes when that is non-zero.
 int launch_gemm_tc(const GemmProblem &p, float *partial, uint32_t *err_word, int sm_count,
                    cudaStream_t stream);
+// One line of text naming the kernel variant, tiling, split and grid launch_gemm_tc would use for this problem
+// on a device with `sm_count` SMs.  Pure host arithmetic: touches no device.
+std::string gemm_tc_describe(const GemmProblem &p, int sm_count);
 // True if the fused second output (GemmProblem::D) can be produced for this problem: no split-K and a
 // 16-byte aligned row pitch.  Otherwise the caller runs the GEMM and the pointwise kernel separately.
 bool gemm_tc_can_fuse_activation(const GemmProblem &p, int sm_count);

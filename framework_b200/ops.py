@@ -11,7 +11,7 @@ from __future__ import annotations
 from typing import Optional, Sequence, Tuple
 
 from . import _lib
-from .tensor import DeviceTensor, current_stream, shape_size
+from .tensor import DeviceTensor, current_stream, row_major_strides, shape_size
 
 
 def broadcast_shape(a: Sequence[int], b: Sequence[int]) -> tuple:
@@ -285,3 +285,18 @@ def device_status() -> int:
 
 def launch_count() -> int:
     return int(_lib.lib().mni_b200_launch_count())
+
+
+def plan_describe(a_shape: Sequence[int], b_shape: Sequence[int], *, a_strides: Optional[Sequence[int]] = None,
+                  b_strides: Optional[Sequence[int]] = None, backward: int = 0, flags: int = 0,
+                  sm_count: int = 148) -> list:
+    """The launches ``matmul`` (backward=0) or ``matmul_backward`` (1; 2 = with the bias gradient) would make for
+    operands of these shapes and element strides (row-major when not given) on a device with `sm_count` SMs:
+    one line of text per launch.  Needs no device -- the planner is host arithmetic."""
+    import ctypes as C
+    va = _lib.make_view(256, a_shape, a_strides if a_strides is not None else row_major_strides(a_shape))
+    vb = _lib.make_view(256, b_shape, b_strides if b_strides is not None else row_major_strides(b_shape))
+    buf = C.create_string_buffer(8192)
+    _lib.check(_lib.lib().mni_b200_plan_describe(C.byref(va), C.byref(vb), int(backward), int(flags), int(sm_count),
+                                                 buf, len(buf)))
+    return buf.value.decode().splitlines()

@@ -265,6 +265,18 @@ MNI_B200_API int mni_b200_workspace_query(const mni_b200_view *a, const mni_b200
 MNI_B200_API int mni_b200_sm_reserve(int sms);
 
 /*
+ * Diagnostics: which kernels mni_b200_matmul_fwd (backward = 0) or mni_b200_matmul_bwd with a contiguous
+ * output gradient and both gradients (backward = 1; 2 = with the bias gradient too) would launch for
+ * these operands and flags on a device with `sm_count` SMs -- one line of text per launch: the product
+ * it belongs to, the kernel, and for the tensor-core kernel its tile width, CTA pairing, contraction
+ * split, balanced tail, grid and the number of pieces a long contraction is summed in.  Operand
+ * pointers are only inspected for alignment.  Pure host arithmetic: touches no device, so the planner
+ * can be checked where there is none.  (No counterpart in the reference.)
+ */
+MNI_B200_API int mni_b200_plan_describe(const mni_b200_view *a, const mni_b200_view *b, int backward,
+                                        uint32_t flags, int sm_count, char *out, size_t out_len);
+
+/*
  * Synchronises `stream` and reports whether any kernel of this library gave up
  * on a bounded wait since the last call (MNI_B200_ERR_TIMEOUT, with the
  * recorded role/stage word in *detail if detail != NULL).  Clears the record.

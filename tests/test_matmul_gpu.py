@@ -441,6 +441,31 @@ def test_small_backward_side_stream_inside_a_cuda_graph(F, oracle):
     F.device_status()
 
 
+def test_plan_description_matches_what_is_launched(F):
+    """`plan_describe` (host arithmetic, checked without a device in the CPU tests) names the launches a call
+    makes: for tensor-path products the launch counter must move by one per described product, plus one for the
+    finish kernel of a split contraction."""
+    import re
+    import torch
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rng = np.random.default_rng(44)
+    for a_shape, b_shape in (((512, 512), (512, 512)), ((1024, 768), (768, 1536)), ((6, 256, 64), (6, 64, 256))):
+        a = F.DeviceTensor.from_numpy(rng.standard_normal(a_shape, dtype=np.float32))
+        b = F.DeviceTensor.from_numpy(rng.standard_normal(b_shape, dtype=np.float32))
+        for backward in (0, 1):
+            lines = [l for l in F.plan_describe(a_shape, b_shape, backward=backward, sm_count=sms) if "tensor" in l]
+            assert len(lines) == (2 if backward else 1), lines
+            expect = sum(1 + (int(re.search(r"splits=(\d+)", l).group(1)) > 1) for l in lines)
+            before = F.launch_count()
+            if backward:
+                g = F.DeviceTensor.from_numpy(rng.standard_normal(a_shape[:-1] + b_shape[-1:], dtype=np.float32))
+                F.matmul_backward(g, a, b)
+            else:
+                F.matmul(a, b)
+            assert F.launch_count() - before == expect, (a_shape, b_shape, backward, lines)
+    F.device_status()
+
+
 def test_scratch_growth_is_refused_while_a_stream_captures(F, oracle):
     """Growing the library-owned scratch frees the old buffer, which a capturing stream must not do and which
     would leave recorded nodes with a dangling address.  A call that would need it during a capture fails with
