@@ -101,6 +101,9 @@ struct KParams {
     int epi_mode;              // EpilogueMode
     int epi_patches;           // staging patches per epilogue warp: TMA stores in flight per warp
     uint32_t idesc;
+    // A tile wider than the output (lone CTA, K-major B): the B box, the lo copy and the MMAs cover only the rows
+    // that exist.  b_rows_live = rows of the B tile that are loaded and split (the tile's width otherwise).
+    int b_rows_live;
     uint32_t a_desc_hi, b_desc_hi;   // upper 32 bits of the smem descriptors (SBO | version | layout)
     uint32_t a_desc_lbo, b_desc_lbo; // LBO field, already shifted into the low word
     uint32_t a_kstep, b_kstep;       // descriptor address advance (16-byte units) per 8-deep k-step
@@ -603,7 +606,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const int k0 = kk * BK;
                     ++armed;
                     if (elect_one()) {
-                        mbar_arrive_expect_tx(full, RAW_BYTES);
+                        mbar_arrive_expect_tx(full, A_BYTES + static_cast<uint32_t>(p.b_rows_live) * BK * 4u);
                         if (armed != p.withhold_at) {        // test hook: a stage that is armed and never filled
                             load_operand(p.a_mode, dstA, &tmA, full, k0, rowA, BM / 32, CHUNK_BYTES, a0, a1, a2);
                             load_operand(p.b_mode, dstA + A_BYTES, &tmB, full, k0, rowB, BNL / 32, CHUNK_BYTES, b0, b1, b2);
@@ -788,15 +791,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const float4 *raw = reinterpret_cast<const float4 *>(stage_base + static_cast<size_t>(stage) * STAGE_BYTES +
                                                                          (TA ? A_BYTES : 0));
                     float4 *lo = const_cast<float4 *>(raw) + N4;
+                    // float4s that hold data: all of them, or A and the live rows of B
+                    const int live4 = N4 - ((BNL - p.b_rows_live) * BK * 4 >> 4);
 #pragma unroll
                     for (int g = 0; g < (FAST ? 0 : PER); g += U) {
                         float4 v[U];
 #pragma unroll
                         for (int u = 0; u < U; ++u)
-                            if (EXACT || tid + (g + u) * NT < N4) v[u] = raw[tid + (g + u) * NT];
+                            if (tid + (g + u) * NT < live4) v[u] = raw[tid + (g + u) * NT];
 #pragma unroll
                         for (int u = 0; u < U; ++u) {
-                            if (!EXACT && tid + (g + u) * NT >= N4) continue;
+                            if (tid + (g + u) * NT >= live4) continue;
                             float4 l;
                             l.x = v[u].x - __uint_as_float(__float_as_uint(v[u].x) & 0xFFFFE000u);
                             l.y = v[u].y - __uint_as_float(__float_as_uint(v[u].y) & 0xFFFFE000u);
@@ -1485,6 +1490,17 @@ Plan make_plan(const GemmProblem &p, int sm_count) {
     return pl;
 }
 
+// N extent of the MMAs.  A lone CTA's tile that is wider than the output multiplies only the columns that exist
+// (units of 16 for a 128-row MMA; whole 32-float chunks when B is read MN-major): an MMA's time is proportional
+// to its N, and a 64-wide tile over a 16-column output would spend three quarters of the tensor pipe on zeros.
+// The rest of the accumulator is never written, and never stored: the epilogue clips at N.
+// MNI_B200_MMA_NARROW=0 keeps full-width MMAs.
+int mma_n_for(const GemmProblem &p, const Plan &pl) {
+    if (pl.cg != 1 || p.N >= pl.bn || env_int("MNI_B200_MMA_NARROW", 1) == 0) return pl.bn;
+    const int64_t unit = p.B.k_major ? 16 : 32;
+    return static_cast<int>(std::min<int64_t>(pl.bn, std::max<int64_t>(unit, (p.N + unit - 1) / unit * unit)));
+}
+
 uint32_t desc_hi_bits(uint32_t sbo_bytes, uint32_t layout_type) {
     // upper word of the shared-memory descriptor: SBO [32,46) | version 1 [46,48) | layout [61,64)
     return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (layout_type << 29);
@@ -1616,11 +1632,11 @@ std::string gemm_tc_describe(const GemmProblem &p0, int sm_count) {
     char buf[320];
     snprintf(buf, sizeof(buf),
              "tensor m=%lld n=%lld k=%lld batch=%lld fold=%lld bn=%d bk=%d pair=%d tmem_a=%d stages=%d splits=%d "
-             "tail=%d grid=%d exchanged=%d single_pass=%d pieces=%d",
+             "tail=%d grid=%d exchanged=%d single_pass=%d pieces=%d mma_n=%d",
              static_cast<long long>(p.M), static_cast<long long>(p.N), static_cast<long long>(p.K),
              static_cast<long long>(p.batch), static_cast<long long>(p.fold), pl.bn, pl.bk, pl.cg == 2 ? 1 : 0,
              pl.ta ? 1 : 0, pl.stages, pl.splits, pl.sk ? 1 : 0, pl.grid, transposed ? 1 : 0, p.fast_tf32 ? 1 : 0,
-             pieces);
+             pieces, mma_n_for(p, pl));
     return buf;
 }
 
@@ -1641,7 +1657,11 @@ int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, in
         return fail(MNI_B200_ERR_ARG, "fused activation requested for a problem that cannot carry it");
     int rc = make_operand_map(&tmA, p.A, BM, pl.bk, &k.a_mode);
     if (rc) return rc;
-    rc = make_operand_map(&tmB, p.B, pl.bn / pl.cg, pl.bk, &k.b_mode);
+    // B rows that exist in a tile wider than the output: with a K-major B (one box of whole rows) only those are
+    // loaded, split and multiplied; the shared memory behind them is never read.
+    const int mma_n = mma_n_for(p, pl);
+    k.b_rows_live = (p.B.k_major && mma_n < pl.bn) ? mma_n : pl.bn / pl.cg;
+    rc = make_operand_map(&tmB, p.B, k.b_rows_live, pl.bk, &k.b_mode);
     if (rc) return rc;
 
     // Epilogue: TMA store when the destination rows are 16-byte aligned, plain stores otherwise.
@@ -1711,7 +1731,7 @@ int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, in
     k.stages = pl.stages;
     k.epi_patches = pl.patches;
     k.idesc = (1u << 4) | (2u << 7) | (2u << 10) | (((p.A.k_major || pl.ta) ? 0u : 1u) << 15) |
-              ((p.B.k_major ? 0u : 1u) << 16) | (static_cast<uint32_t>(pl.bn >> 3) << 17) |
+              ((p.B.k_major ? 0u : 1u) << 16) | (static_cast<uint32_t>(mma_n >> 3) << 17) |
               (static_cast<uint32_t>((BM * pl.cg) >> 4) << 24);
     // K-major tile: rows of BK floats, 8-row groups SBO apart, swizzle span = one row.
     // MN-major tile: 32-float chunks of BK k-rows (LBO apart); the 32-byte-unit swizzle repeats every
