@@ -484,7 +484,8 @@ __device__ __forceinline__ void load_operand(int mode, uint32_t dst, const CUten
 // memory and no MMA re-reads A from it, which is what bounds narrow tiles otherwise.
 // SK = true compiles the balanced-tail epilogue (parking / reducing shared tiles) in; the other
 // instantiations carry none of its code or registers.
-template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false, bool SK = false>
+// SG = 2 (TA only): the split warps work as two groups on alternate k-blocks (see the split role).
+template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false, bool SK = false, int SG = 1>
 __global__ void __launch_bounds__(32 * (2 + NS + kEpiWarps), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
@@ -537,7 +538,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(bar_full + 8u * s, 1);
-            mbar_init(bar_xform + 8u * s, CG * NS);        // one arrival per split warp, of both CTAs for a pair
+            mbar_init(bar_xform + 8u * s, CG * NS / SG);   // one arrival per split warp (of the k-block's group; of both CTAs for a pair)
             mbar_init(bar_empty + 8u * s, 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -731,13 +732,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // In single-pass mode there is nothing to split; for a CTA pair these warps still relay "my
         // CTA's tile has landed" to the leader's barrier.
         if (!FAST || CG == 2) {
-            const int tid = threadIdx.x - 64;
+            // With A in tensor memory one k-block is a serial chain per warp (barrier wake-up, loads, split, tensor-
+            // memory stores and their completion, fence, arrival: ~600 cycles, measured) that the eight warps walk in
+            // lockstep, each on one k-half of its lane quarter's rows (SG = 1).  With SG = 2 they work as two groups
+            // of four (one warp per lane quarter) on alternate k-blocks instead: twice the work per warp and k-block,
+            // two k-blocks in flight.  The host picks SG = 2 for long contractions.
+            static_assert(SG == 1 || (SG == 2 && TA), "two split groups exist for the tensor-memory A variants only");
+            constexpr int GROUPS = SG;
+            const int group = TA ? (warp - 2) >> 2 : 0;   // SG = 1: the k-half this warp splits; SG = 2: its group
+            const int tid = (threadIdx.x - 64) & (32 * NS / GROUPS - 1);   // index within the group
             int stage = 0;
+            int kb = 0;                                   // k-blocks this CTA has seen: the group takes those of its parity
             uint32_t phase = 0;
             bool ok = true;
             long long waited = 0;
             constexpr int N4 = (TA ? B_BYTES : RAW_BYTES) >> 4;   // float4 count of what gets a lo copy
-            constexpr int NT = 32 * NS;                   // split threads
+            constexpr int NT = 32 * NS / GROUPS;          // split threads that share one k-block
             constexpr int PER = (N4 + NT - 1) / NT;       // float4s per thread (the last round may be partial)
             constexpr bool EXACT = N4 % NT == 0;
             constexpr int U = !EXACT ? 1 : (PER % 4 == 0) ? 4 : (PER % 2 == 0 ? 2 : 1);
@@ -746,13 +756,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             while (ok && work_next(p, wi, wt)) {
                 const int iters = wt.it1 - wt.it0;
                 for (int it = 0; it < iters; ++it) {
+                    if (SG == 2 && ((kb++ & 1) != group)) {    // the other group's k-block
+                        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
                     ok = mbar_wait(bar_full + 8u * stage, phase, abort_flag, p.err, 0x400u | stage, waited, timed, p.wait_cycles);
                     if (!ok) break;
                     if constexpr (TA) {
-                        // A: this thread owns row (lane quarter of its warp) and 16 of the 32 k columns.
-                        const uint8_t *sa = stage_base + static_cast<size_t>(stage) * STAGE_BYTES;
-                        const int half = (warp - 2) >> 2;
-                        const int row = (warp & 3) * 32 + lane;
+                      // A: this thread owns a row (lane quarter of its warp), 16 of the 32 k columns at a time.
+                      const uint8_t *sa = stage_base + static_cast<size_t>(stage) * STAGE_BYTES;
+                      const int row = (warp & 3) * 32 + lane;
+#pragma unroll
+                      for (int h = 0; h < SG; ++h) {
+                        const int half = SG == 2 ? h : group;
                         uint32_t hi[16], lo16[16];
                         if (p.a_mode == kKMajor) {
                             // 128-byte rows, 16-byte chunk c of row r sits at chunk c ^ (r % 8)
@@ -784,8 +800,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         __syncwarp();                      // tcgen05.st is warp-collective
                         tmem_st16(ta, hi);
                         tmem_st16(ta + BK, lo16);
-                        tmem_st_wait();
-                        tc_fence_before();
+                      }
                     }
                     // TA: only the B tile gets a lo copy in shared memory (it sits right behind the raw B tile).
                     const float4 *raw = reinterpret_cast<const float4 *>(stage_base + static_cast<size_t>(stage) * STAGE_BYTES +
@@ -809,6 +824,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             l.w = v[u].w - __uint_as_float(__float_as_uint(v[u].w) & 0xFFFFE000u);
                             lo[tid + (g + u) * NT] = l;
                         }
+                    }
+                    if constexpr (TA) {                       // the stores above complete while the B tile was split
+                        tmem_st_wait();
+                        tc_fence_before();
                     }
                     // Every thread publishes its writes to the async proxy; one lane per warp then arrives
                     // (a remote arrival crosses SMs, so they are kept to one per warp).
@@ -1506,7 +1525,7 @@ uint32_t desc_hi_bits(uint32_t sbo_bytes, uint32_t layout_type) {
     return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (layout_type << 29);
 }
 
-template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false, bool SK = false>
+template <int BN, int BK, bool FAST, int NS, int CG, bool TA = false, bool SK = false, int SG = 1>
 cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
                            const CUtensorMap &tmD, const KParams &k, cudaStream_t stream) {
     // The shared-memory opt-in is an attribute of the function on ONE device: set once per device of the process
@@ -1517,7 +1536,7 @@ cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtenso
     if (attr != cudaSuccess) return attr;
     const uint64_t bit = 1ull << (dev & 63);
     if ((opted_in.load(std::memory_order_acquire) & bit) == 0) {
-        attr = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FAST, NS, CG, TA, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        attr = cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FAST, NS, CG, TA, SK, SG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024);
         if (attr != cudaSuccess) return attr;
         opted_in.fetch_or(bit, std::memory_order_release);
@@ -1536,7 +1555,7 @@ cudaError_t launch_variant(const Plan &pl, const CUtensorMap &tmA, const CUtenso
     attrs[1].val.clusterDim.z = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = CG == 2 ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK, FAST, NS, CG, TA, SK>, tmA, tmB, tmC, tmD, k);
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, BK, FAST, NS, CG, TA, SK, SG>, tmA, tmB, tmC, tmD, k);
 }
 
 }  // namespace
@@ -1772,16 +1791,29 @@ int launch_gemm_tc(const GemmProblem &p0, float *partial, uint32_t *err_word, in
         if (pl.grid * 3 * kEpiWarps > kSkFlagCount) return fail(MNI_B200_ERR_CUDA, "balanced-tail flag array too small");
     }
 
+    // Two split groups pay when the k-loop is long enough for the second k-block in flight to matter (measured:
+    // K = 512 per unit 33.6 -> 32.8 us per attention-shaped product, 128 k-blocks 57.9 -> 54.4 us; four k-blocks per
+    // unit are no faster).  MNI_B200_SPLIT_GROUPS=1/2 forces either.
+    int split_groups = 1;
+    if (pl.ta) {
+        const long long unit_iters = (static_cast<long long>(k.fold) * k.kiters + pl.splits - 1) / pl.splits;
+        const int sg_env = env_int("MNI_B200_SPLIT_GROUPS", 0);
+        split_groups = (sg_env == 1 || sg_env == 2) ? sg_env : (unit_iters >= 12 ? 2 : 1);
+    }
     cudaError_t e = cudaErrorInvalidValue;
     if (pl.sk) {
-        if (pl.ta && pl.bn == 64) e = launch_variant<64, 32, false, 8, 1, true, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+        if (pl.ta && pl.bn == 64 && split_groups == 2) e = launch_variant<64, 32, false, 8, 1, true, true, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
+        else if (pl.ta && pl.bn == 64) e = launch_variant<64, 32, false, 8, 1, true, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+        else if (pl.ta && pl.bn == 128 && split_groups == 2) e = launch_variant<128, 32, false, 8, 1, true, true, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
         else if (pl.ta && pl.bn == 128) e = launch_variant<128, 32, false, 8, 1, true, true>(pl, tmA, tmB, tmC, tmD, k, stream);
         else if (!p.fast_tf32 && pl.bk == 16) e = launch_variant<256, 16, false, 8, 2, false, true>(pl, tmA, tmB, tmC, tmD, k, stream);
         else if (!p.fast_tf32 && pl.bk == 32) e = launch_variant<256, 32, false, 8, 2, false, true>(pl, tmA, tmB, tmC, tmD, k, stream);
         else if (pl.bk == 16) e = launch_variant<256, 16, true, 4, 2, false, true>(pl, tmA, tmB, tmC, tmD, k, stream);
         else e = launch_variant<256, 32, true, 4, 2, false, true>(pl, tmA, tmB, tmC, tmD, k, stream);
     } else if (pl.ta) {
-        if (pl.bn == 64) e = launch_variant<64, 32, false, 8, 1, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+        if (pl.bn == 64 && split_groups == 2) e = launch_variant<64, 32, false, 8, 1, true, false, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
+        else if (pl.bn == 64) e = launch_variant<64, 32, false, 8, 1, true>(pl, tmA, tmB, tmC, tmD, k, stream);
+        else if (split_groups == 2) e = launch_variant<128, 32, false, 8, 1, true, false, 2>(pl, tmA, tmB, tmC, tmD, k, stream);
         else e = launch_variant<128, 32, false, 8, 1, true>(pl, tmA, tmB, tmC, tmD, k, stream);
     }
 #define MNI_VARIANT(BN_, BK_)                                                                         \
