@@ -14,7 +14,9 @@
 //               low 13 mantissa bits of a TF32 operand (tests/test_matmul_gpu.py pins that).
 //               Narrow tiles (BN <= 128, lone CTA) instead move A into tensor memory: each thread
 //               reads 16 k-values of its row and stores hi and lo with tcgen05.st; only B keeps a
-//               lo copy in shared memory.
+//               lo copy in shared memory.  For long contractions the eight warps take alternate
+//               k-blocks as two groups of four (SG = 2), so two k-blocks are in flight.  When the
+//               tile is wider than the output, MMAs, B box and lo copy cover only the live columns.
 //   warp 1      issues tcgen05.mma.kind::tf32 per 8-deep k-step: lo*hi, hi*lo, hi*hi into one f32
 //               accumulator in TMEM ("3xTF32"); one MMA on the raw tile in single-pass mode.  The
 //               warp runs its loop uniformly and predicates the issue with elect.sync, and it reads

@@ -93,6 +93,7 @@ def test_attention_shapes_strided_key_and_narrow_outputs(plan):
     assert (dkt["bn"], dkt["tmem_a"], dkt["grid"], dkt["exchanged"]) == (64, 1, 74, 1)
     o_fwd = tensor_plan(plan((8, 12, 512, 512), (8, 12, 512, 64)), "forward")
     assert (o_fwd["bn"], o_fwd["tmem_a"], o_fwd["pair"], o_fwd["splits"], o_fwd["grid"]) == (64, 1, 0, 1, 148)
+    assert o_fwd["mma_n"] == 64
     o_bwd = plan((8, 12, 512, 512), (8, 12, 512, 64), backward=1)
     ds, dv = tensor_plan(o_bwd, "grad_a"), tensor_plan(o_bwd, "grad_b")
     assert (ds["bn"], ds["pair"], ds["grid"]) == (256, 1, 74)
@@ -125,6 +126,7 @@ def test_few_rows_take_the_streaming_kernels(plan):
         assert bwd["grad_a"][0][0] == "streaming" and bwd["grad_b"][0][0] == "streaming"
     f = tensor_plan(plan((16, 4096), (4096, 4096)), "forward")
     assert (f["exchanged"], f["m"], f["n"], f["bn"], f["tmem_a"], f["splits"]) == (1, 4096, 16, 64, 1, 4)
+    assert f["mma_n"] == 16                              # a 64-wide tile over 16 columns multiplies 16
     bwd = plan((16, 4096), (4096, 4096), backward=1)
     assert tensor_plan(bwd, "grad_a")["exchanged"] == 1
     dw = tensor_plan(bwd, "grad_b")
@@ -140,6 +142,21 @@ def test_flags_and_undescribable_views(plan):
     strided = plan((256, 256), (256, 256), a_strides=(512, 2))
     assert any("gather of a strided operand" in line for line in strided)
     assert tensor_plan(plan((256, 256), (256, 256), flags=_lib.force_split_k(3)), "forward")["splits"] == 3
+
+
+def test_mma_width_follows_the_output_width(plan):
+    """Lone-CTA tiles wider than the output: MMAs in units of 16 columns for a K-major B (here b is given
+    transposed, so its rows are contiguous along the contraction), whole 32-float chunks for an MN-major one."""
+    from framework_b200 import _lib
+    t = _lib.FORCE_TENSOR_PATH
+    k_major = {n: tensor_plan(plan((128, 256), (256, n), b_strides=(1, 256), flags=t), "forward")["mma_n"]
+               for n in (8, 16, 24, 40, 64, 100)}
+    assert k_major == {8: 16, 16: 16, 24: 32, 40: 48, 64: 64, 100: 64}      # 100 columns: two 64-wide tiles
+    mn_major = {n: tensor_plan(plan((128, 256), (256, n), flags=t), "forward")["mma_n"] for n in (8, 40, 64, 100)}
+    assert mn_major == {8: 32, 40: 64, 64: 64, 100: 64}
+    # CTA pairs keep full-width MMAs
+    wide = tensor_plan(plan((32768, 256), (256, 200), flags=t), "forward")
+    assert (wide["bn"], wide["pair"], wide["mma_n"]) == (256, 1, 256)
 
 
 def test_errors_are_the_calls_own(plan):
