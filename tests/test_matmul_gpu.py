@@ -441,6 +441,42 @@ def test_small_backward_side_stream_inside_a_cuda_graph(F, oracle):
     F.device_status()
 
 
+@pytest.mark.parametrize("m,k,n", [(256, 512, 16), (300, 200, 24), (128, 2048, 40), (384, 96, 8)])
+@pytest.mark.parametrize("b_transposed", [False, True])
+def test_narrow_outputs_multiply_only_live_columns(F, oracle, m, k, n, b_transposed):
+    """Tiles wider than the output: the MMAs are issued N-wide (in units of 16, or whole 32-float chunks when B is
+    read along N), and for a B that is contiguous along the contraction only its live rows are loaded and split.
+    The accumulator columns beyond are never written, so nothing of them may reach the output: plain forward,
+    with bias, accumulated onto a non-zero C, with a forced split of the contraction, single pass, and both
+    gradients -- all inside guard zones."""
+    rng = np.random.default_rng(1000 * n + m)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    bias = rng.standard_normal((n,), dtype=np.float32)
+    T = F._lib.FORCE_TENSOR_PATH
+    if b_transposed:                              # storage [n, k]: rows contiguous along the contraction
+        b = rng.standard_normal((n, k), dtype=np.float32)
+        perm = (1, 0)
+    else:
+        b = rng.standard_normal((k, n), dtype=np.float32)
+        perm = None
+    for flags, kw in ((T, {}), (T, {"bias": bias}), (T | F._lib.force_split_k(3), {}),
+                      (T | F._lib.PRECISION_TF32, {"fast": True})):
+        _check_fwd(F, oracle, a, b, perm_b=perm, flags=flags, **kw)
+    # C += a.b on a C that holds data
+    H = oracle.HostTensor
+    hb = H.from_array(b) if perm is None else oracle.permute(H.from_array(b), perm)
+    db = _dev(F, b) if perm is None else _dev(F, b).permute(perm)
+    c0 = rng.standard_normal((m, n), dtype=np.float32)
+    gout = Guarded(F, (m, n), init=c0)
+    F.matmul(_dev(F, a), db, flags=T | F._lib.ACCUMULATE_C, out=gout.tensor)
+    F.device_status()
+    gout.check("accumulated output", fully_written=False)
+    ref = oracle.matmul(H.from_array(a), hb).numpy() + c0
+    assert float(np.max(np.abs(gout.tensor.numpy() - ref))) <= tol_3xtf32(k, a, b) + 1e-6
+    g = rng.standard_normal((m, n), dtype=np.float32)
+    _check_bwd(F, oracle, a, b, g, perm_b=perm, flags=T)
+
+
 def test_plan_description_matches_what_is_launched(F):
     """`plan_describe` (host arithmetic, checked without a device in the CPU tests) names the launches a call
     makes: for tensor-path products the launch counter must move by one per described product, plus one for the
