@@ -242,3 +242,95 @@ def test_softmax_reference_checks(oracle):
     assert np.max(np.abs(dx[1])) < 1e-7                   # a constant upstream gradient gives zero
     j = np.diag(want[0]) - np.outer(want[0], want[0])     # Jacobian of softmax
     assert np.max(np.abs(dx[0] - j @ g[0].astype(np.float64))) < 1e-6
+
+
+def _numeric_grad(f, x, eps=1e-3):
+    """Central differences of the scalar f with respect to every element of x (float64)."""
+    g = np.zeros_like(x, dtype=np.float64)
+    flat, gf = x.reshape(-1), g.reshape(-1)
+    for i in range(flat.size):
+        keep = flat[i]
+        flat[i] = keep + eps
+        hi = f()
+        flat[i] = keep - eps
+        lo = f()
+        flat[i] = keep
+        gf[i] = (hi - lo) / (2 * eps)
+    return g
+
+
+@pytest.mark.parametrize("shape_a,shape_b", [
+    ((3, 4), (4, 2)),                  # 2-D
+    ((2, 3, 4), (2, 4, 5)),            # batched
+    ((3, 2, 4), (4, 5)),               # weight shared by every batch: grad_b is summed over the batches
+    ((2, 3, 3, 4), (1, 3, 4, 2)),      # b broadcast along the leading batch dim (batch % 3 = true broadcasting here)
+])
+def test_backward_is_the_derivative_of_the_forward(oracle, shape_a, shape_b):
+    """The reference's tests hold no backward values (test/autograd.test.ts:41-46 only asks that a gradient
+    exists), so the backward restatement is pinned here by what it must be: the derivative of
+    loss = sum(grad * forward(a, b)), taken by central differences in float64 through NumPy's own broadcasting
+    matmul -- a computation that shares nothing with ops/matmul.rs:200-222 (transposes, products, unbroadcast).
+    Shapes where each operand broadcasts along a different batch dim are left out on purpose: there the
+    reference's forward indexes `batch % operand_batch` (ops/matmul.rs:55-56) while its backward un-broadcasts
+    by position (utils.rs:39-66), so its own backward is not the derivative of its own forward; the oracle
+    follows the reference in both (test_non_simple_broadcast_uses_modulo_indexing)."""
+    O = oracle
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal(shape_a)
+    b = rng.standard_normal(shape_b)
+    g = rng.standard_normal(np.matmul(a, b).shape)
+    loss = lambda: float(np.sum(g * np.matmul(a, b)))   # noqa: E731
+    na, nb = _numeric_grad(loss, a), _numeric_grad(loss, b)
+    H = O.HostTensor
+    da, db = O.matmul_backward(H.from_array(g.astype(np.float32)), H.from_array(a.astype(np.float32)),
+                               H.from_array(b.astype(np.float32)), threads=1)
+    assert da.shape == shape_a and db.shape == shape_b
+    np.testing.assert_allclose(da.numpy(), na, rtol=2e-4, atol=2e-4)
+    np.testing.assert_allclose(db.numpy(), nb, rtol=2e-4, atol=2e-4)
+
+
+def test_permuted_operand_backward_is_the_derivative(oracle):
+    """S = Q . K^T with K^T a stride-only permute of K (the attention-shaped configuration): the gradient that
+    reaches K through permute_backward (ops/layout.rs:162-195) is the derivative with respect to K's storage."""
+    O = oracle
+    rng = np.random.default_rng(12)
+    q = rng.standard_normal((2, 3, 4))
+    k = rng.standard_normal((2, 5, 4))
+    g = rng.standard_normal((2, 3, 5))
+    loss = lambda: float(np.sum(g * np.matmul(q, np.swapaxes(k, 1, 2))))   # noqa: E731
+    nk = _numeric_grad(loss, k)
+    H = O.HostTensor
+    kt = O.permute(H.from_array(k.astype(np.float32)), (0, 2, 1))
+    _, dkt = O.matmul_backward(H.from_array(g.astype(np.float32)), H.from_array(q.astype(np.float32)), kt, threads=1)
+    dk = O.permute_backward(dkt, (0, 2, 1), (2, 5, 4))
+    assert dk.shape == (2, 5, 4)
+    np.testing.assert_allclose(dk.numpy(), nk, rtol=2e-4, atol=2e-4)
+
+
+def test_pointwise_backwards_are_derivatives(oracle):
+    """bias + GELU (ops/fused.rs:279-392, tanh form), softmax (ops/norm.rs:95-123) and the bias add
+    (ops/elementwise.rs:199-211): each backward against central differences of its own forward."""
+    O = oracle
+    rng = np.random.default_rng(13)
+    H = O.HostTensor
+    x = rng.standard_normal((3, 5))
+    bias = rng.standard_normal((5,))
+    g = rng.standard_normal((3, 5))
+
+    def gelu_loss():
+        return float(np.sum(g * O.bias_gelu(H.from_array(x.astype(np.float32)),
+                                            H.from_array(bias.astype(np.float32))).numpy().astype(np.float64)))
+    dx, dbias = O.bias_gelu_backward(H.from_array(g.astype(np.float32)), H.from_array(x.astype(np.float32)),
+                                     H.from_array(bias.astype(np.float32)))
+    # the forward runs in f32, so the step is large and the tolerance loose
+    np.testing.assert_allclose(dx.numpy(), _numeric_grad(gelu_loss, x, eps=1e-2), rtol=5e-3, atol=5e-3)
+    np.testing.assert_allclose(dbias.numpy(), _numeric_grad(gelu_loss, bias, eps=1e-2), rtol=5e-3, atol=5e-3)
+
+    s_in = rng.standard_normal((2, 3, 6))
+    gs = rng.standard_normal((2, 3, 6))
+    for dim in (-1, 1):
+        def sm_loss():
+            return float(np.sum(gs * O.softmax(s_in.astype(np.float32), dim).astype(np.float64)))
+        sm = O.softmax(s_in.astype(np.float32), dim)
+        ds = O.softmax_backward(gs.astype(np.float32), sm, dim)
+        np.testing.assert_allclose(ds, _numeric_grad(sm_loss, s_in, eps=1e-2), rtol=5e-3, atol=5e-3)
